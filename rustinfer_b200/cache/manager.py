@@ -30,17 +30,28 @@ class CacheGroup:
 
 @dataclass
 class CacheLayout:
-    """Run entries sorted into groups; `entry_cache[i]` = (group, index in group) or None."""
+    """Run entries sorted into groups; `entry_cache[i]` = (group, index in group), None, or for a
+    mixer that declared several needs a list of such pairs in the order of its needs."""
     groups: List[CacheGroup]
-    entry_cache: List[Optional[Tuple[int, int]]]
+    entry_cache: List[Any]
     entry_writes: List[bool]
 
     @classmethod
     def from_needs(cls, needs: Sequence[Tuple[int, Optional[CacheNeed], Optional[int]]]) -> "CacheLayout":
         groups: List[CacheGroup] = []
         by_need: Dict[CacheNeed, int] = {}
-        entry_cache: List[Optional[Tuple[int, int]]] = []
+        entry_cache: List[Any] = []
         writes: List[bool] = []
+
+        def place(i: int, need: CacheNeed) -> Tuple[int, int]:
+            g = by_need.get(need)
+            if g is None:
+                g = len(groups)
+                by_need[need] = g
+                groups.append(CacheGroup(need, []))
+            groups[g].entries.append(i)
+            return (g, len(groups[g].entries) - 1)
+
         for i, (_layer, need, cache_of) in enumerate(needs):
             if cache_of is not None:
                 entry_cache.append(entry_cache[cache_of])
@@ -49,14 +60,10 @@ class CacheLayout:
             writes.append(True)
             if need is None:
                 entry_cache.append(None)
-                continue
-            g = by_need.get(need)
-            if g is None:
-                g = len(groups)
-                by_need[need] = g
-                groups.append(CacheGroup(need, []))
-            groups[g].entries.append(i)
-            entry_cache.append((g, len(groups[g].entries) - 1))
+            elif isinstance(need, (tuple, list)):
+                entry_cache.append([place(i, n) for n in need])
+            else:
+                entry_cache.append(place(i, need))
         return cls(groups, entry_cache, writes)
 
     def paged_groups(self) -> List[int]:
@@ -229,11 +236,12 @@ class CacheManager:
         if self._blocks_for(r.length) > min((len(t) for t in r.tables.values()), default=1 << 60):
             raise RuntimeError(f"request {request_id!r} committed tokens it holds no pages for")
         for g, table in r.tables.items():
-            window = self.layout.groups[g].need.window
-            if window is None:
+            need = self.layout.groups[g].need
+            if need.window is None and need.block is None:
                 continue
-            # the next token sits at position `length` and sees keys from length - window + 1
-            keep_from = max(0, r.length - window + 1) // self.page_size
+            # the next token sits at position `length`; pages before the first key it sees (the
+            # window's start, or the start of its block of positions) are given back
+            keep_from = need.first_key_kept(r.length) // self.page_size
             first = r.first_live[g]
             if keep_from > first:
                 self.pools[g].free(table[first:keep_from])

@@ -37,19 +37,20 @@ def supported_architectures() -> List[str]:
 
 
 def resolve_architecture(cfg: Mapping[str, Any]) -> ArchitectureFamily:
-    """`architectures[0]` and `model_type` are looked up by exact (case-folded) name;
+    """`architectures[0]`, `model_type` and `architecture` are looked up by exact (case-folded) name;
     an unknown model is an error that lists what is supported."""
     hints: List[str] = []
     archs = cfg.get("architectures")
     if isinstance(archs, (list, tuple)) and archs and isinstance(archs[0], str):
         hints.append(archs[0])
-    if isinstance(cfg.get("model_type"), str):
-        hints.append(cfg["model_type"])
+    for key in ("model_type", "architecture"):           # some families name themselves in one string
+        if isinstance(cfg.get(key), str):
+            hints.append(cfg[key])
     for h in hints:
         fam = _BY_NAME.get(h.lower())
         if fam is not None:
             return fam
-    shown = ", ".join(repr(h) for h in hints) or "<missing model_type/architectures>"
+    shown = ", ".join(repr(h) for h in hints) or "<missing model_type/architectures/architecture>"
     raise ConfigError(f"unsupported model {shown}; supported: {', '.join(supported_architectures())}")
 
 

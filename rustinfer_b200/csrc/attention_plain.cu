@@ -1,12 +1,14 @@
 // Paged causal GQA attention over the cache, any head size (compiled for one
-// RI_HEAD_DIM, a multiple of 16), storage fp32 or bf16, all arithmetic fp32 on CUDA
-// cores.  It is the attention of the true-32-bit path and the fallback of the bf16
+// RI_HEAD_DIM and, where values have a size of their own, one RI_VALUE_DIM), storage fp32
+// or bf16, all arithmetic fp32 on CUDA cores.  It is the attention of the true-32-bit path and the fallback of the bf16
 // path; it serves whole prompts, portions of prompts and single decoded tokens alike.
 //
 // What it computes is RustInfer's paged attention
 // (crates/infer-core/src/ports/fused_ops.rs:484-523): the query at position p of a
 // request sees keys 0..p (with a window w: p-w+1..p), kv head = q head / (Hq/Hkv),
-// scores (q.k)*scale, softmax with the maximum subtracted.  The reference has no fp32
+// scores (q.k)*scale, softmax with the maximum subtracted.  With a block size c the query
+// at p sees only keys from floor(p/c)*c on (blocks are counted from position 0 of the
+// request): a lower bound like the window's, and both may be given.  The reference has no fp32
 // attention on the GPU (crates/infer-backend-cuda/src/kernels/flash_attn_gqa/flash_attn_gqa.h:30).
 //
 // One CTA of 128 threads handles a tile of 16 consecutive query tokens of one request
@@ -19,16 +21,21 @@
 #error "compile with -DRI_HEAD_DIM=<head size>"
 #endif
 
+#ifndef RI_VALUE_DIM
+#define RI_VALUE_DIM RI_HEAD_DIM
+#endif
+
 namespace {
-constexpr int HD = RI_HEAD_DIM;
-static_assert(HD % 16 == 0 && HD >= 16 && HD <= 512, "head size must be a multiple of 16 up to 512");
+constexpr int HD = RI_HEAD_DIM;                // size of a query and a key
+constexpr int VD = RI_VALUE_DIM;               // size of a value and of a head's output
+static_assert(HD >= 1 && HD <= 512 && VD >= 1 && VD <= 512, "head sizes up to 512");
 constexpr int QT = 16;                         // query rows per CTA
 constexpr int KC = HD <= 128 ? 64 : 32;        // keys per chunk
 constexpr int THREADS = 128;
 constexpr int NCOL = KC / 8;                   // score columns per thread
-constexpr int NACC = HD / 8;                   // output dims per thread
+constexpr int NACC = (VD + 7) / 8;             // output dims per thread
 constexpr int QS = HD + 1, KS = HD + 1, PS = KC + 1;
-constexpr size_t SMEM_FLOATS = (size_t)QT * QS + (size_t)KC * KS + (size_t)KC * HD + (size_t)QT * PS;
+constexpr size_t SMEM_FLOATS = (size_t)QT * QS + (size_t)KC * KS + (size_t)KC * VD + (size_t)QT * PS;
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
@@ -36,14 +43,14 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const T* __restrict__ cache, const int* __restrict__ block_table,
                        int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                        const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
-                       int Hq, int Hkv, int page_size, float scale, int window) {
+                       int Hq, int Hkv, int page_size, float scale, int window, int block) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
     float* Qs = smem;
     float* Ks = Qs + QT * QS;
     float* Vs = Ks + KC * KS;
-    float* Ps = Vs + KC * HD;
+    float* Ps = Vs + KC * VD;
 
     const int tile = blockIdx.x, h = blockIdx.y;
     const int b = tile_entry[tile];
@@ -66,9 +73,13 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
 
     const bool row_valid = row < rows_here;
     const int p_row = pos0 + j0 + row;                   // this row's position
-    const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
+    int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
     const int p_last = pos0 + j0 + rows_here - 1;        // last key any row of the tile sees
-    const int lo_tile = window > 0 ? max(0, pos0 + j0 - window + 1) : 0;
+    int lo_tile = window > 0 ? max(0, pos0 + j0 - window + 1) : 0;   // first key its first row sees
+    if (block > 0) {
+        lo_row = max(lo_row, (p_row / block) * block);
+        lo_tile = max(lo_tile, ((pos0 + j0) / block) * block);
+    }
 
     float m = -INFINITY, l = 0.f;
     float acc[NACC];
@@ -76,21 +87,31 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
     const int* bt = block_table + (size_t)b * table_stride;
-    const size_t head_step = (size_t)page_size * HD;
+    // a page: keys [kv head][slot][HD], then values [kv head][slot][VD]
+    const size_t page_elems = (size_t)Hkv * page_size * (HD + VD);
+    const size_t v_base = (size_t)Hkv * page_size * HD + (size_t)g * page_size * VD;
+    const size_t k_base = (size_t)g * page_size * HD;
     for (int kb = (lo_tile / KC) * KC; kb <= p_last; kb += KC) {
         __syncthreads();                                 // previous chunk's Vs/Ps reads are done
         for (int e = tid; e < KC * HD; e += THREADS) {
             const int kk = e / HD, d = e - kk * HD;
             const int key = kb + kk;
-            float kval = 0.f, vval = 0.f;
+            float kval = 0.f;
             if (key >= lo_tile && key <= p_last) {
                 const int page = bt[key / page_size], off = key % page_size;
-                const size_t base = ((size_t)(page * 2) * Hkv + g) * head_step + (size_t)off * HD + d;
-                kval = to_f32<T>(cache[base]);
-                vval = to_f32<T>(cache[base + (size_t)Hkv * head_step]);
+                kval = to_f32<T>(cache[(size_t)page * page_elems + k_base + (size_t)off * HD + d]);
             }
             Ks[kk * KS + d] = kval;
-            Vs[kk * HD + d] = vval;
+        }
+        for (int e = tid; e < KC * VD; e += THREADS) {
+            const int kk = e / VD, d = e - kk * VD;
+            const int key = kb + kk;
+            float vval = 0.f;
+            if (key >= lo_tile && key <= p_last) {
+                const int page = bt[key / page_size], off = key % page_size;
+                vval = to_f32<T>(cache[(size_t)page * page_elems + v_base + (size_t)off * VD + d]);
+            }
+            Vs[kk * VD + d] = vval;
         }
         __syncthreads();
 
@@ -135,16 +156,18 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
         const float* pr = Ps + row * PS;
         for (int kk = 0; kk < KC; ++kk) {
             const float p = pr[kk];
-            const float* vr = Vs + kk * HD + l8;
+            const float* vr = Vs + kk * VD + l8;
 #pragma unroll
-            for (int i = 0; i < NACC; ++i) acc[i] = fmaf(p, vr[8 * i], acc[i]);
+            for (int i = 0; i < NACC; ++i)
+                if (VD % 8 == 0 || l8 + 8 * i < VD) acc[i] = fmaf(p, vr[8 * i], acc[i]);
         }
     }
     if (row_valid) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        T* o = out + (size_t)(q_begin + j0 + row) * out_stride + (size_t)h * HD + l8;
+        T* o = out + (size_t)(q_begin + j0 + row) * out_stride + (size_t)h * VD + l8;
 #pragma unroll
-        for (int i = 0; i < NACC; ++i) o[8 * i] = from_f32<T>(acc[i] * inv);
+        for (int i = 0; i < NACC; ++i)
+            if (VD % 8 == 0 || l8 + 8 * i < VD) o[8 * i] = from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -152,7 +175,7 @@ template <typename T>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* cache,
            const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
            const int* tile_entry, const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
-           float scale, int window, cudaStream_t s) {
+           float scale, int window, int block, cudaStream_t s) {
     static bool configured = false;
     const size_t smem = SMEM_FLOATS * sizeof(float);
     if (!configured) {
@@ -164,30 +187,32 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* c
     dim3 grid(n_tiles, Hq);
     RI_CHECKED(ri_launch(attention_plain_kernel<T>, dim3(grid), dim3(THREADS), smem, s, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)cache, block_table, table_stride,
-        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window));
+        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window, block));
     return ri_launch_status();
 }
 }  // namespace
 
 RI_API int ri_attention_plain_head_dim() { return HD; }
+RI_API int ri_attention_plain_value_dim() { return VD; }
 RI_API int ri_attention_plain_tile_rows() { return QT; }
 
-// q: rows of `q_stride` elements, head h at column h*HD; out likewise with out_stride.
-// cache: one layer, [page][K|V][kv head][slot][HD].  tile_entry[i] = batch entry of tile i
+// q: rows of `q_stride` elements, head h at column h*HD; out rows of out_stride, head h at
+// column h*VD.  cache: one layer, per page the keys [kv head][slot][HD] and then the values
+// [kv head][slot][VD] ([page][K|V][kv head][slot][HD] when the two sizes are equal).  tile_entry[i] = batch entry of tile i
 // (-1: skip), tile_q0[i] = its first query row within that entry.
 RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_stride,
                               const void* cache, int dtype, const int* block_table, int table_stride,
                               const int* cu_q, const int* kv_len, const int* tile_entry,
                               const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
-                              float scale, int window, void* stream) {
+                              float scale, int window, int block, void* stream) {
     if (n_tiles <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RI_BF16)
         return launch<bf16>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
-                            kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, s);
+                            kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, s);
     return launch<float>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
-                         kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, s);
+                         kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, s);
 }
 
 RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }

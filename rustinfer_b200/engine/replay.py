@@ -20,7 +20,7 @@ import sys
 from typing import List, Optional
 
 PAGE_SIZE = 16                      # divides 64, the unit --max-tokens is counted in
-MAX_LIVE = 8
+MAX_LIVE = 4                        # requests live at one time (state slots)
 
 
 def main(argv: Optional[List[str]] = None) -> int:

@@ -295,7 +295,8 @@ class ModelRunner:
         per_page = 0
         for g in self.layout.groups:
             if isinstance(g.need, PagedKV):
-                per_page += len(g.entries) * 2 * g.need.num_kv_heads * self.page_size * g.need.head_dim * esize
+                per_page += (len(g.entries) * g.need.num_kv_heads * self.page_size
+                             * (g.need.head_dim + g.need.v_dim) * esize)
         cap = self.max_batch_seqs * self.max_pages_per_request
         if per_page == 0:
             return 1
@@ -313,8 +314,12 @@ class ModelRunner:
             n = len(g.entries)
             if isinstance(g.need, PagedKV):
                 self._paged_index[gi] = len(self._paged_index)
-                t = torch.zeros((n, self.num_pages, 2, g.need.num_kv_heads, self.page_size, g.need.head_dim),
-                                dtype=self.dtype, device=self.device)
+                if g.need.v_dim == g.need.head_dim:
+                    shape = (n, self.num_pages, 2, g.need.num_kv_heads, self.page_size, g.need.head_dim)
+                else:                           # a page's keys, then its values, which have another size
+                    shape = (n, self.num_pages,
+                             g.need.num_kv_heads * self.page_size * (g.need.head_dim + g.need.v_dim))
+                t = torch.zeros(shape, dtype=self.dtype, device=self.device)
             elif isinstance(g.need, FixedState):
                 # one row more than there are slots: padding rows of a captured step point there
                 t = torch.zeros((n, self.max_batch_seqs + 1) + tuple(g.need.shape),
@@ -322,17 +327,21 @@ class ModelRunner:
             else:
                 raise TypeError(f"unknown cache need {g.need!r}")
             self.group_storage.append(t)
+        def view(i: int, loc) -> Any:
+            gi, idx = loc
+            if isinstance(self.layout.groups[gi].need, PagedKV):
+                return PagedLayerCache(self.group_storage[gi][idx], self._paged_index[gi],
+                                       self.layout.entry_writes[i])
+            return StateLayerCache(self.group_storage[gi][idx])
+
         self.entry_caches: List[Any] = []
         for i, loc in enumerate(self.layout.entry_cache):
             if loc is None:
                 self.entry_caches.append(None)
-                continue
-            gi, idx = loc
-            if isinstance(self.layout.groups[gi].need, PagedKV):
-                self.entry_caches.append(PagedLayerCache(self.group_storage[gi][idx], self._paged_index[gi],
-                                                         self.layout.entry_writes[i]))
+            elif isinstance(loc, list):         # a mixer with several needs gets a tuple of caches
+                self.entry_caches.append(tuple(view(i, l) for l in loc))
             else:
-                self.entry_caches.append(StateLayerCache(self.group_storage[gi][idx]))
+                self.entry_caches.append(view(i, loc))
 
     def cache_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.group_storage)

@@ -9,7 +9,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts import attention, ffn, norm, rope, stem_tail  # noqa: F401  (registers the built-in parts)
+from ..parts import attention, ffn, linear_attention, norm, parallel, rope, stem_tail  # noqa: F401  (registers the built-in parts)
 from ..parts.base import EMBEDDINGS, HEADS, NORMS, BuildContext, CacheNeed, ParamDecl, StepContext, StepIndex
 from ..parts.block import Block, Hidden
 from ..parts.spec import ModelSpec
@@ -83,7 +83,7 @@ class Decoder:
         # (crates/infer-worker/src/models/decoder.rs:245-262)
         self.head.offer_shared(self.embed.shared_table())
         self.head.load(pick(s.head_name, self.head))
-        self.final_norm.load({n: tensors[s.final_norm_name + n] for n in self.final_norm.param_decls()})
+        self.final_norm.load(pick(s.final_norm_name, self.final_norm))
         for block, ls in zip(self.blocks, s.layers):
             for role, part in block.roles().items():
                 part.load({n: tensors[ls.names[role] + n] for n in part.param_decls()

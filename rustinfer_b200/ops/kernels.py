@@ -394,8 +394,11 @@ def decode_chain(products: Sequence[ChainProduct], rope: Optional[ChainRope], to
 def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                     cu_q: torch.Tensor, kv_len: torch.Tensor, tile_entry: torch.Tensor,
                     tile_q0: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: Optional[int]) -> None:
-    """q [T, >=Hq*hd] (may be a column view of the qkv buffer), out [T, Hq*hd]."""
+                    scale: float, window: Optional[int], block: Optional[int] = None,
+                    value_dim: Optional[int] = None) -> None:
+    """q [T, >=Hq*hd] (may be a column view of the qkv buffer), out [T, Hq*vd].  `block`: a query
+    sees only the keys of its own block of that many positions (counted from 0).  `value_dim`:
+    size of a value where it is not the keys'; the cache is then [pages, Hkv*page*(hd+vd)]."""
     require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_q0)
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
                  (tile_entry, "tile_entry"), (tile_q0, "tile_q0")):
@@ -403,16 +406,211 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
     if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != cache.dtype or out.dtype != cache.dtype:
         raise KernelError("attention: q, out and cache share a dtype; q and out have unit column stride")
     _contig(cache, "cache")
-    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
-        raise KernelError("attention: cache must be [pages, 2, Hkv, page, head_dim]")
+    vd = value_dim or head_dim
+    page_size = paged_cache_page_size(cache, num_kv_heads, head_dim, vd)
     if num_heads % num_kv_heads:
         raise KernelError("attention: heads must be a multiple of kv heads")
-    lib = L.attention_plain(head_dim)
+    lib = L.attention_plain(head_dim, vd)
     check(lib.ri_attention_plain(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache),
                                  dtype_code(cache.dtype), _p(block_table), block_table.stride(0),
                                  _p(cu_q), _p(kv_len), _p(tile_entry), _p(tile_q0), tile_entry.numel(),
-                                 num_heads, num_kv_heads, cache.shape[3], float(scale),
-                                 int(window) if window else 0, stream_ptr()), "attention_plain")
+                                 num_heads, num_kv_heads, page_size, float(scale),
+                                 int(window) if window else 0, int(block) if block else 0, stream_ptr()),
+          "attention_plain")
+
+
+def paged_cache_page_size(cache: torch.Tensor, num_kv_heads: int, head_dim: int, value_dim: int) -> int:
+    """Tokens a page of `cache` holds: [pages, 2, Hkv, page, hd] when keys and values have one size,
+    [pages, Hkv * page * (hd + vd)] (a page's keys, then its values) when they differ."""
+    if cache.dim() == 5:
+        if value_dim != head_dim or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+            raise KernelError("attention: cache must be [pages, 2, Hkv, page, head_dim]")
+        return cache.shape[3]
+    per_token = num_kv_heads * (head_dim + value_dim)
+    if cache.dim() != 2 or cache.shape[1] % per_token:
+        raise KernelError("attention: cache must be [pages, Hkv * page * (head_dim + value_dim)]")
+    return cache.shape[1] // per_token
+
+
+# ------------------------------------------------ parts of decoders that are not the Llama shape
+def embed_sinusoid(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, freq: torch.Tensor,
+                   out: torch.Tensor) -> None:
+    """out[t,:] (fp32) = table[ids[t],:] + the sinusoidal vector of positions[t]; `freq` (float64,
+    [ceil(d/2)]) holds the angular frequency of every (sin, cos) pair."""
+    require_cuda(ids, positions, table, freq, out)
+    _i32(ids, "ids"); _i32(positions, "positions"); _contig(table, "table"); _contig(out, "out")
+    d = table.shape[1]
+    if out.dtype != torch.float32 or out.shape != (ids.numel(), d):
+        raise KernelError(f"embed_sinusoid: out must be fp32 [{ids.numel()}, {d}]")
+    if freq.dtype != torch.float64 or freq.numel() != (d + 1) // 2 or positions.numel() < ids.numel():
+        raise KernelError("embed_sinusoid: freq is float64 [ceil(d/2)], one position per id")
+    check(L.core().ri_embed_sinusoid(_p(ids), _p(positions), _p(table), dtype_code(table.dtype), _p(freq), _p(out),
+                                     ids.numel(), d, table.shape[0], stream_ptr()), "embed_sinusoid")
+
+
+def sandwich_norm(h: torch.Tensor, delta: Optional[torch.Tensor], post_w: Optional[torch.Tensor],
+                  post_b: Optional[torch.Tensor], next_w: Optional[torch.Tensor], next_b: Optional[torch.Tensor],
+                  out: Optional[torch.Tensor], eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """Layer norm around a sublayer.  h (fp32 [T,d]) += LN(delta; post_w, post_b) when `delta` is given;
+    out = LN(h; next_w, next_b) when `out` is given.  With `rows` (int32 [R]) only those rows are
+    read, out is [R,d] and h is left as it is."""
+    require_cuda(h, delta, post_w, post_b, next_w, next_b, out, rows)
+    d = h.shape[-1]
+    _contig(h, "h"); _i32(rows, "rows")
+    if h.dtype != torch.float32:
+        raise KernelError("sandwich_norm: the residual stream is fp32")
+    n_rows = h.shape[0] if rows is None else rows.numel()
+    ws = [w for w in (post_w, post_b, next_w, next_b) if w is not None]
+    for w in ws:
+        _contig(w, "norm weight")
+        if w.numel() != d or w.dtype != ws[0].dtype:
+            raise KernelError(f"sandwich_norm: norm weights have {d} elements and one dtype")
+    act = None
+    if delta is not None:
+        _contig(delta, "delta")
+        if delta.shape != h.shape:
+            raise KernelError("sandwich_norm: delta has h's shape")
+        act = delta.dtype
+    if out is not None:
+        _contig(out, "out")
+        if out.shape != (n_rows, d) or (act is not None and out.dtype != act):
+            raise KernelError(f"sandwich_norm: out must be [{n_rows}, {d}] of delta's dtype")
+        act = out.dtype
+    if act is None:
+        return
+    check(L.core().ri_sandwich_norm(_p(h), _p(delta), _p(post_w), _p(post_b), _p(next_w), _p(next_b), _p(out),
+                                    dtype_code(act), dtype_code(ws[0].dtype) if ws else 0, _p(rows), n_rows, d,
+                                    float(eps), stream_ptr()), "sandwich_norm")
+
+
+def head_norm_scatter(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                      value_norm: bool, eps: float, slot_of_token: Optional[torch.Tensor],
+                      cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                      value_dim: int) -> None:
+    """qkv [T, Hq*hd + Hkv*hd + Hkv*vd]: q and k of every head are divided by their root mean square
+    and multiplied by a weight [hd] shared by the heads (None: left as they are), v by its root
+    mean square when `value_norm`; q in place, k and v into the cache at slot_of_token[t]
+    (page*page_size + offset; < 0 skips)."""
+    require_cuda(qkv, q_weight, k_weight, slot_of_token, cache)
+    _i32(slot_of_token, "slot_of_token")
+    if qkv.stride(1) != 1 or qkv.shape[1] != num_heads * head_dim + num_kv_heads * (head_dim + value_dim):
+        raise KernelError("head_norm_scatter: qkv must be [T, Hq*hd + Hkv*(hd+vd)] with unit column stride")
+    ws = [w for w in (q_weight, k_weight) if w is not None]
+    for w in ws:
+        _contig(w, "weight")
+        if w.numel() != head_dim or w.dtype != ws[0].dtype:
+            raise KernelError(f"head_norm_scatter: norm weights have {head_dim} elements and one dtype")
+    page = 1
+    if cache is not None:
+        _contig(cache, "cache")
+        if cache.dtype != qkv.dtype:
+            raise KernelError("head_norm_scatter: cache has qkv's dtype")
+        page = paged_cache_page_size(cache, num_kv_heads, head_dim, value_dim)
+    check(L.core().ri_head_norm_scatter(_p(qkv), dtype_code(qkv.dtype), qkv.stride(0), _p(q_weight), _p(k_weight),
+                                        dtype_code(ws[0].dtype) if ws else 0, 1 if value_norm else 0, float(eps),
+                                        _p(slot_of_token), _p(cache), qkv.shape[0], num_heads, num_kv_heads,
+                                        head_dim, value_dim, page, stream_ptr()), "head_norm_scatter")
+
+
+GATE_SILU, GATE_SIGMOID = 0, 1
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, weight_per_head: bool, act: int,
+                    eps: float, out: torch.Tensor, num_heads: int, value_dim: int) -> None:
+    """out = o / rms_head(o) * weight * act(gate): o fp32 [T, H*vd], gate [T, >=H*vd] (may be a column
+    view), weight [vd] shared by the heads or [H*vd]."""
+    require_cuda(o, gate, weight, out)
+    _contig(o, "o"); _contig(out, "out"); _contig(weight, "weight")
+    T = o.shape[0]
+    if o.dtype != torch.float32 or o.shape != (T, num_heads * value_dim) or out.shape != o.shape:
+        raise KernelError("gated_head_norm: o is fp32 [T, H*vd] and out has its shape")
+    if gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] != o.shape[1] or gate.dtype != out.dtype:
+        raise KernelError("gated_head_norm: gate is [T, H*vd] of out's dtype with unit column stride")
+    if weight.numel() != (num_heads * value_dim if weight_per_head else value_dim):
+        raise KernelError("gated_head_norm: weight size")
+    check(L.core().ri_gated_head_norm(_p(o), _p(gate), gate.stride(0), _p(weight), dtype_code(weight.dtype),
+                                      1 if weight_per_head else 0, int(act), float(eps), _p(out),
+                                      dtype_code(out.dtype), T, num_heads, value_dim, stream_ptr()), "gated_head_norm")
+
+
+ACT_GELU_ERF, ACT_TANH, ACT_GELU_TANH = 0, 1, 2
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: int) -> None:
+    require_cuda(x, out)
+    _contig(x, "x"); _contig(out, "out")
+    if x.shape != out.shape or x.dtype != out.dtype:
+        raise KernelError("activation: out has x's shape and dtype")
+    check(L.core().ri_activation(_p(x), _p(out), dtype_code(x.dtype), x.numel(), int(kind), stream_ptr()), "activation")
+
+
+def scaled_sum(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torch.Tensor) -> None:
+    """out = sa * a + sb * b."""
+    require_cuda(a, b, out)
+    _contig(a, "a"); _contig(b, "b"); _contig(out, "out")
+    if a.shape != b.shape or a.shape != out.shape or a.dtype != b.dtype or a.dtype != out.dtype:
+        raise KernelError("scaled_sum: a, b and out share shape and dtype")
+    check(L.core().ri_scaled_sum(_p(a), _p(b), float(sa), float(sb), _p(out), dtype_code(a.dtype), a.numel(),
+                                 stream_ptr()), "scaled_sum")
+
+
+def _scan_common(state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor,
+                 T: int, H: int, dk: int, dv: int, what: str) -> None:
+    _i32(cu_q, "cu_q"); _i32(state_slots, "state_slots")
+    _contig(state, "state"); _contig(out, "out")
+    if state.dtype != torch.float32 or state.dim() != 4 or tuple(state.shape[1:]) != (H, dk, dv):
+        raise KernelError(f"{what}: state is fp32 [slots, {H}, {dk}, {dv}]")
+    if out.dtype != torch.float32 or out.shape != (T, H * dv):
+        raise KernelError(f"{what}: out is fp32 [T, H*dv]")
+
+
+def _cols(t: torch.Tensor, T: int, n: int, dtype: torch.dtype, what: str) -> None:
+    if t.dim() != 2 or t.shape != (T, n) or t.stride(1) != 1 or t.dtype != dtype:
+        raise KernelError(f"{what} must be [{T}, {n}] {dtype} with unit column stride")
+
+
+def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: Optional[torch.Tensor],
+               q_scale: float, tau: float, out: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+               state_slots: torch.Tensor, entries: int, num_heads: int, key_dim: int, value_dim: int) -> None:
+    """Gated linear attention over every entry's tokens in order, from and into state[slot]:
+    S = diag(sigmoid(z + z_bias)^(1/tau)) S + k v^T, out = S^T (q * q_scale).  q, k [T, H*dk], v [T, H*dv]
+    (column views allowed), z fp32 [T, H*dk]."""
+    require_cuda(q, k, v, z, z_bias, out, state, cu_q, state_slots)
+    T, H, dk, dv = q.shape[0], num_heads, key_dim, value_dim
+    _scan_common(state, out, cu_q, state_slots, T, H, dk, dv, "gated_scan")
+    _cols(q, T, H * dk, q.dtype, "gated_scan: q"); _cols(k, T, H * dk, q.dtype, "gated_scan: k")
+    _cols(v, T, H * dv, q.dtype, "gated_scan: v"); _cols(z, T, H * dk, torch.float32, "gated_scan: z")
+    if z_bias is not None and z_bias.numel() != H * dk:
+        raise KernelError("gated_scan: z_bias has H*dk elements")
+    check(L.recurrent(dk).ri_gated_scan(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(z), z.stride(0),
+                                        _p(z_bias), dtype_code(q.dtype),
+                                        dtype_code(z_bias.dtype) if z_bias is not None else 0, float(q_scale),
+                                        1.0 / float(tau), _p(out), _p(state), _p(cu_q), _p(state_slots), int(entries),
+                                        H, dv, stream_ptr()), "gated_scan")
+
+
+def delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, za: torch.Tensor, za_bias: Optional[torch.Tensor],
+               zw: torch.Tensor, zw_bias: Optional[torch.Tensor], decay_rate: float, unit_eps: float,
+               out: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, entries: int,
+               num_heads: int, key_dim: int, value_dim: int) -> None:
+    """Delta rule with a decay, over every entry's tokens in order, from and into state[slot]:
+    S = diag(w) S - (a * u)(u^T S) + k v^T, out = S^T r, with u = k / sqrt(|k|^2 + unit_eps),
+    w = exp(-decay_rate * sigmoid(zw + zw_bias)), a = sigmoid(za + za_bias).  zw is fp32."""
+    require_cuda(r, k, v, za, za_bias, zw, zw_bias, out, state, cu_q, state_slots)
+    T, H, dk, dv = r.shape[0], num_heads, key_dim, value_dim
+    _scan_common(state, out, cu_q, state_slots, T, H, dk, dv, "delta_scan")
+    for t, n, what in ((r, H * dk, "r"), (k, H * dk, "k"), (v, H * dv, "v"), (za, H * dk, "za")):
+        _cols(t, T, n, r.dtype, "delta_scan: " + what)
+    _cols(zw, T, H * dk, torch.float32, "delta_scan: zw")
+    biases = [b for b in (za_bias, zw_bias) if b is not None]
+    for b in biases:
+        if b.numel() != H * dk or b.dtype != biases[0].dtype:
+            raise KernelError("delta_scan: biases have H*dk elements and one dtype")
+    check(L.recurrent(dk).ri_delta_scan(_p(r), r.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(za), za.stride(0),
+                                        _p(za_bias), _p(zw), zw.stride(0), _p(zw_bias), dtype_code(r.dtype),
+                                        dtype_code(biases[0].dtype) if biases else 0, float(decay_rate),
+                                        float(unit_eps), _p(out), _p(state), _p(cu_q), _p(state_slots), int(entries),
+                                        H, dv, stream_ptr()), "delta_scan")
 
 
 def _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim):

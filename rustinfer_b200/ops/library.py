@@ -38,10 +38,18 @@ _SIGNATURES = {
     "ri_gemm_tc_rope": [_P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "ri_decode_chain": [_P, _I, _P, _I, _P, _P, _I, _P],
     "ri_decode_chain_fits": [_P, _I, _I, _I],
-    "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "ri_embed_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
+    "ri_sandwich_norm": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _F, _P],
+    "ri_head_norm_scatter": [_P, _I, _I, _P, _P, _I, _I, _F, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ri_gated_head_norm": [_P, _P, _I, _P, _I, _I, _I, _F, _P, _I, _I, _I, _I, _P],
+    "ri_activation": [_P, _P, _I, _L, _I, _P],
+    "ri_scaled_sum": [_P, _P, _F, _F, _P, _I, _L, _P],
+    "ri_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _F, _P, _P, _P, _P, _I, _I, _I, _P],
+    "ri_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _F, _F, _P, _P, _P, _P, _I, _I, _I, _P],
 }
 
-_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "sampling.cu"]
+_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "sampling.cu", "sequence_parts.cu"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 
 
@@ -89,11 +97,22 @@ def core() -> ctypes.CDLL:
     return _load("ri_core", _CORE_SOURCES)
 
 
-def attention_plain(head_dim: int) -> ctypes.CDLL:
-    if head_dim % 16 != 0 or not 16 <= head_dim <= 512:
-        raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to 512, "
-                          f"got {head_dim}")
-    return _load(f"ri_attention_plain_hd{head_dim}", ["attention_plain.cu"], [f"RI_HEAD_DIM={head_dim}"])
+def attention_plain(head_dim: int, value_dim: Optional[int] = None) -> ctypes.CDLL:
+    """The fp32-arithmetic attention for keys of `head_dim` and values of `value_dim` (default: the same)."""
+    value_dim = value_dim or head_dim
+    if not (1 <= head_dim <= 512 and 1 <= value_dim <= 512):
+        raise KernelError(f"the plain attention kernel takes head sizes up to 512, got {head_dim} and {value_dim}")
+    if value_dim == head_dim:
+        return _load(f"ri_attention_plain_hd{head_dim}", ["attention_plain.cu"], [f"RI_HEAD_DIM={head_dim}"])
+    return _load(f"ri_attention_plain_hd{head_dim}_vd{value_dim}", ["attention_plain.cu"],
+                 [f"RI_HEAD_DIM={head_dim}", f"RI_VALUE_DIM={value_dim}"])
+
+
+def recurrent(key_dim: int) -> ctypes.CDLL:
+    """The linear-attention recurrences (gated and delta rule) for one key size."""
+    if not 1 <= key_dim <= 512:
+        raise KernelError(f"the recurrence kernels take key sizes up to 512, got {key_dim}")
+    return _load(f"ri_recurrent_k{key_dim}", ["recurrent.cu"], [f"RI_KDIM={key_dim}"])
 
 
 def gemm_tc() -> ctypes.CDLL:

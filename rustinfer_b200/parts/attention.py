@@ -23,7 +23,17 @@ from .spec import PartSpec
 class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window (None: all keys),
     position (PartSpec of a rotary encoding, or None), own_kv (False: the layer projects no
-    keys or values and reads the cache another layer wrote)."""
+    keys or values and reads the cache another layer wrote).
+
+    Further options, each None or absent by default: `value_dim` (size of a value and of a head's
+    output where it is not head_dim), `block` (a query sees only keys of its own block of that
+    many positions, counted from position 0 of the request), `qk_norm_eps` (q and k of every head
+    are divided by their root mean square over head_dim and multiplied by the weights
+    `q_norm` / `k_norm` [head_dim], shared by the heads), `value_norm_eps` (v of every head is divided
+    by its root mean square; it is cached so), `tensor_names` (local name -> name in the file, for
+    checkpoints that call q_proj.weight and the others something else).  A mixer with any of the
+    first four runs on the fp32-arithmetic attention kernel in both precisions: scores, softmax
+    weights and the weighted sum of values are 32-bit there."""
 
     graph_safe = True
     adds_to_residual = True
@@ -37,9 +47,22 @@ class GQAAttention(Mixer):
         self.scale = float(p["scale"])
         self.window = int(p["window"]) if p.get("window") else None
         self.own_kv = bool(p.get("own_kv", True))
+        self.vd = int(p.get("value_dim") or self.hd)
+        self.block = int(p["block"]) if p.get("block") else None
+        self.qk_norm_eps = float(p["qk_norm_eps"]) if p.get("qk_norm_eps") is not None else None
+        self.value_norm_eps = float(p["value_norm_eps"]) if p.get("value_norm_eps") is not None else None
+        self.tensor_names = dict(p.get("tensor_names") or {})
+        # options only the plain kernel and the head-norm kernel serve
+        self.general = (self.vd != self.hd or self.block is not None or self.qk_norm_eps is not None
+                        or self.value_norm_eps is not None)
         if self.Hq % self.Hkv:
             raise ValueError(f"{self.Hq} heads are not a multiple of {self.Hkv} kv heads")
-        if self.hd % 16 or not 16 <= self.hd <= 512:
+        if self.general:
+            if not (1 <= self.hd <= 512 and 1 <= self.vd <= 512):
+                raise ValueError(f"head sizes {self.hd}, {self.vd}: the attention kernel takes sizes up to 512")
+            if self.qk_norm_eps is not None and self.value_norm_eps is not None and self.qk_norm_eps != self.value_norm_eps:
+                raise ValueError("the norms of q, k and of v share one eps")
+        elif self.hd % 16 or not 16 <= self.hd <= 512:
             raise ValueError(f"head_dim {self.hd}: the attention kernels take multiples of 16 up to 512")
         pos = p.get("position")
         self.position_spec: Optional[PartSpec] = pos
@@ -47,23 +70,31 @@ class GQAAttention(Mixer):
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
 
+    def _name(self, local: str) -> str:
+        return self.tensor_names.get(local, local)
+
     def param_decls(self) -> Dict[str, ParamDecl]:
         q, kv = self.Hq * self.hd, self.Hkv * self.hd
-        d = {"q_proj.weight": ParamDecl((q, self.hidden)),
-             "o_proj.weight": ParamDecl((self.hidden, q))}
+        d = {self._name("q_proj.weight"): ParamDecl((q, self.hidden)),
+             self._name("o_proj.weight"): ParamDecl((self.hidden, self.Hq * self.vd))}
         if self.own_kv:
-            d["k_proj.weight"] = ParamDecl((kv, self.hidden))
-            d["v_proj.weight"] = ParamDecl((kv, self.hidden))
+            d[self._name("k_proj.weight")] = ParamDecl((kv, self.hidden))
+            d[self._name("v_proj.weight")] = ParamDecl((self.Hkv * self.vd, self.hidden))
+        if self.qk_norm_eps is not None:
+            d[self._name("q_norm")] = ParamDecl((self.hd,), init="ones")
+            if self.own_kv:
+                d[self._name("k_norm")] = ParamDecl((self.hd,), init="ones")
         return d
 
     def cache_need(self):
-        return PagedKV(self.Hkv, self.hd, self.window)
+        return PagedKV(self.Hkv, self.hd, self.window, value_dim=self.vd if self.vd != self.hd else None,
+                       block=self.block)
 
     def prepare(self, ctx: BuildContext) -> None:
         super().prepare(ctx)
         # bf16 runs on the tensor-core kernels (head sizes up to 256); fp32, and larger heads,
         # on the plain fp32-arithmetic kernel
-        self.use_mma = ctx.dtype == torch.bfloat16 and self.hd <= L.MMA_MAX_HEAD_DIM
+        self.use_mma = ctx.dtype == torch.bfloat16 and self.hd <= L.MMA_MAX_HEAD_DIM and not self.general
         # steps of 512 tokens or more: rotary encoding and cache write inside the q,k,v product
         self.fuse_rope = (ctx.dtype == torch.bfloat16 and self.hd in (64, 128)
                           and os.environ.get("RUSTINFER_B200_FUSE_ROPE", "1") != "0")
@@ -104,12 +135,17 @@ class GQAAttention(Mixer):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         # q, k, v fused by rows into one matrix, gate rows first
         # (crates/infer-worker/src/models/loader.rs:419-454)
-        parts = [tensors["q_proj.weight"]]
+        parts = [tensors[self._name("q_proj.weight")]]
         if self.own_kv:
-            parts += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
+            parts += [tensors[self._name("k_proj.weight")], tensors[self._name("v_proj.weight")]]
         dt = torch.float32 if any(t.dtype == torch.float32 for t in parts) else parts[0].dtype
         self.qkv = Linear(torch.cat([t.to(dt) for t in parts], dim=0), self.ctx.num_sms)
-        self.o = Linear(tensors["o_proj.weight"], self.ctx.num_sms)
+        self.o = Linear(tensors[self._name("o_proj.weight")], self.ctx.num_sms)
+        self.q_norm = self.k_norm = None
+        if self.qk_norm_eps is not None:
+            self.q_norm = tensors[self._name("q_norm")].contiguous()
+            if self.own_kv:
+                self.k_norm = tensors[self._name("k_norm")].to(self.q_norm.dtype).contiguous()
 
     def _project_out(self, out: torch.Tensor, residual: Optional[torch.Tensor]):
         if residual is not None and self.o.add_into(out, residual):
@@ -131,6 +167,16 @@ class GQAAttention(Mixer):
                               self.Hq, self.Hkv if writes else 0, self.hd):
                 return self._project_out(self.attend(q, step, cache), residual)
         qkv = self.qkv(x, out_dtype=self.ctx.dtype)
+        if self.general:
+            if self.position is not None or not self.own_kv:
+                raise NotImplementedError("head norms, a value size of its own and the block mask are built "
+                                          "for mixers without rotation that project their own keys")
+            # per-head norms of q, k, v in fp32, then keys and values into their pages
+            K.head_norm_scatter(qkv, self.q_norm, self.k_norm, self.value_norm_eps is not None,
+                                self.qk_norm_eps if self.qk_norm_eps is not None else (self.value_norm_eps or 0.0),
+                                g.slot_of_token if writes else None, cache.kv if writes else None,
+                                self.Hq, self.Hkv, self.hd, self.vd)
+            return self._project_out(self.attend(qkv[:, : self.Hq * self.hd], step, cache), residual)
         if self.position is not None:
             # a layer that reads another's cache has only the q projection: qkv is q alone
             K.rope_scatter(qkv, step.positions, self.position.cos,
@@ -161,11 +207,11 @@ class GQAAttention(Mixer):
         T = step.num_tokens
         g = step.groups[cache.group]
         if out is None:
-            out = torch.empty((T, self.Hq * self.hd), dtype=self.ctx.dtype, device=q.device)
+            out = torch.empty((T, self.Hq * self.vd), dtype=self.ctx.dtype, device=q.device)
         if not self.use_mma:
             tile_entry, tile_q0 = step.index(self._tiles)
             K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
-                              self.Hq, self.Hkv, self.hd, self.scale, self.window)
+                              self.Hq, self.Hkv, self.hd, self.scale, self.window, self.block, self.vd)
             return out
         (single,) = step.index(self._single)
         if single.numel():

@@ -33,7 +33,8 @@ from .spec import PartSpec
 @dataclass(frozen=True)
 class ParamDecl:
     """A tensor a part owns: its shape, how the random-weights mode fills it
-    ("normal": N(0, std); "ones": 1, or 1 + N(0, std) when norms are perturbed)."""
+    ("normal": N(0, std); "ones" / "zeros": 1 / 0, plus N(0, std) when norms are perturbed).  A size
+    of -1 is one that only the file's tensor gives (the rank of a low-rank pair, say)."""
     shape: Tuple[int, ...]
     init: str = "normal"
     optional: bool = False
@@ -41,10 +42,28 @@ class ParamDecl:
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every token (or of the last `window` tokens) in pages."""
+    """Keys and values of every token (or of the last `window` tokens, or of the tokens of the
+    current block of `block` positions) in pages.  `value_dim`: size of a value where it is not
+    the keys' `head_dim`; a page then holds its keys [kv head][slot][head_dim] followed by its
+    values [kv head][slot][value_dim]."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+    block: Optional[int] = None
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
+
+    def first_key_kept(self, length: int) -> int:
+        """The first position the token at position `length` (the next one) can still see."""
+        lo = 0
+        if self.window:
+            lo = max(lo, length - self.window + 1)
+        if self.block:
+            lo = max(lo, length // self.block * self.block)
+        return lo
 
 
 @dataclass(frozen=True)
@@ -55,6 +74,8 @@ class FixedState:
 
 
 CacheNeed = Union[PagedKV, FixedState]
+# a mixer made of several (attention beside a recurrence, say) needs several: a tuple of them
+CacheNeeds = Union[CacheNeed, Tuple[CacheNeed, ...]]
 
 
 @dataclass
@@ -234,7 +255,9 @@ class Head(Part):
 class Mixer(Part):
     graph_safe = True                   # in steps of single tokens, forward reads only device tensors
 
-    def cache_need(self) -> Optional[CacheNeed]:
+    def cache_need(self) -> Optional[CacheNeeds]:
+        """What the mixer keeps between steps: None, one need, or a tuple of needs (its `forward`
+        then gets a tuple of caches in the same order)."""
         return None
 
     def step_indices(self) -> Sequence[StepIndex]:

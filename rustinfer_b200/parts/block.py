@@ -76,7 +76,30 @@ def _pre_norm(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
         hidden.pending = block.ffn.forward(x, step)
 
 
-ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm}
+def _sandwich(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
+    """A norm before and a norm after each sublayer:
+
+        h += post_mixer_norm(mixer(mixer_norm(h)));  h += post_ffn_norm(ffn(ffn_norm(h)))
+
+    (the second line only when the layer has a feed-forward).  The norms after the sublayers go
+    by the roles `post_mixer_norm` and `post_ffn_norm` in `extra_norms`.  A sublayer's output stays
+    pending as a `NormedDelta`; the next norm that reads the stream, of this layer, the next or
+    the model's last, norms it, adds it and norms the sum in one kernel."""
+    from .norm import NormedDelta
+    post_mixer, post_ffn = block.extra_norms.get("post_mixer_norm"), block.extra_norms.get("post_ffn_norm")
+    if block.mixer_norm is None or post_mixer is None:
+        raise ValueError("the sandwich arrangement wants a norm before and a norm after the mixer")
+    x = block.mixer_norm.add_norm(hidden.stream, hidden.pending)
+    hidden.pending = NormedDelta(block.mixer.forward(x, step, cache), post_mixer)
+    if block.ffn is None:
+        return
+    if block.ffn_norm is None or post_ffn is None:
+        raise ValueError("the sandwich arrangement wants a norm before and a norm after the feed-forward")
+    x = block.ffn_norm.add_norm(hidden.stream, hidden.pending)
+    hidden.pending = NormedDelta(block.ffn.forward(x, step), post_ffn)
+
+
+ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm, "sandwich": _sandwich}
 
 
 def register_arrangement(name: str, fn: Callable) -> None:

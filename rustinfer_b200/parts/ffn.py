@@ -55,3 +55,41 @@ class SwiGLU(FeedForward):
         if residual is not None and self.down.add_into(m, residual):
             return None
         return self.down(m, out_dtype=self.ctx.dtype)
+
+
+_ACTIVATIONS = {"gelu": K.ACT_GELU_ERF, "gelu_erf": K.ACT_GELU_ERF, "tanh": K.ACT_TANH, "gelu_tanh": K.ACT_GELU_TANH}
+
+
+@register_feed_forward("dense_mlp")
+class DenseMLP(FeedForward):
+    """down( act(up(x)) ) without a gate.  params: hidden_size, intermediate_size, activation
+    ("gelu": with erf; "gelu_tanh"; "tanh"), up_name / down_name (tensor names, default
+    "up_proj.weight" / "down_proj.weight").  The activation is computed in fp32."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        act = str(params.get("activation", "gelu"))
+        if act not in _ACTIVATIONS:
+            raise ValueError(f"activation {act!r}: known are {sorted(_ACTIVATIONS)}")
+        self.act = _ACTIVATIONS[act]
+        self.up_name = str(params.get("up_name", "up_proj.weight"))
+        self.down_name = str(params.get("down_name", "down_proj.weight"))
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {self.up_name: ParamDecl((self.inter, self.hidden)),
+                self.down_name: ParamDecl((self.hidden, self.inter))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = Linear(tensors[self.up_name], self.ctx.num_sms)
+        self.down = Linear(tensors[self.down_name], self.ctx.num_sms)
+
+    def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None):
+        u = self.up(x, out_dtype=self.ctx.dtype)
+        K.activation(u, u, self.act)
+        if residual is not None and self.down.add_into(u, residual):
+            return None
+        return self.down(u, out_dtype=self.ctx.dtype)

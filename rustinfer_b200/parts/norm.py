@@ -4,6 +4,7 @@ crates/infer-backend-cuda/src/kernels/rmsnorm/rmsnorm.cu:52-113).  Sum of square
 scale and the residual sum are fp32."""
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Dict, Optional
 
 import torch
@@ -33,3 +34,64 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=h.device)
         K.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
         return out
+
+
+@dataclass
+class NormedDelta:
+    """A sublayer's output that is to pass through `norm` before it is added to the stream (a
+    block with a norm after each sublayer leaves this as its pending delta)."""
+    delta: torch.Tensor
+    norm: "LayerNorm"
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w + b over the last axis, var the mean of the squared
+    deviations; mean, variance, scale and the residual sum are fp32.  params: size, eps, bias
+    (True: the file has a bias; False: none; None: used when the file has one).  The weight's
+    tensor is named by the part's prefix alone, the bias by prefix + `.b`, unless `weight_name` /
+    `bias_name` say otherwise.
+
+    `add_norm` takes as `delta` a tensor (added as it is), None, or a `NormedDelta` (normed by the
+    norm it names, then added): one kernel does that norm, the add and this norm."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.has_bias = params.get("bias", True)
+        self.weight_name = str(params.get("weight_name", ""))
+        self.bias_name = str(params.get("bias_name", ".b"))
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        d = {self.weight_name: ParamDecl((self.size,), init="ones")}
+        if self.has_bias is None or self.has_bias:
+            d[self.bias_name] = ParamDecl((self.size,), init="zeros", optional=self.has_bias is None)
+        return d
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].contiguous()
+        b = tensors.get(self.bias_name)
+        self.bias = b.to(self.weight.dtype).contiguous() if b is not None else None
+
+    def add_norm(self, h, delta, rows=None):
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=h.device)
+        if isinstance(delta, NormedDelta):
+            post = delta.norm
+            if post.eps != self.eps:            # two norms of one kernel share eps; else two launches
+                post.add_into(h, delta.delta)
+                K.sandwich_norm(h, None, None, None, self.weight, self.bias, out, self.eps, rows)
+            else:
+                K.sandwich_norm(h, delta.delta, post.weight, post.bias, self.weight, self.bias, out, self.eps, rows)
+            return out
+        if delta is not None:
+            K.residual_add(h, delta)
+        K.sandwich_norm(h, None, None, None, self.weight, self.bias, out, self.eps, rows)
+        return out
+
+    def add_into(self, h: torch.Tensor, delta: torch.Tensor) -> None:
+        """h += LN(delta)."""
+        K.sandwich_norm(h, delta, self.weight, self.bias, None, None, None, self.eps)

@@ -1,0 +1,64 @@
+"""Two mixers side by side on one input: out = left_scale * left(x) + right_scale * right(x).
+
+Each side is a mixer of any registered kind with its own tensors (under the prefixes `left.` and
+`right.` unless the spec names others) and its own cache: the part declares both sides' needs
+and hands each side the cache that belongs to it.  The reference engine has one mixer per block
+(crates/infer-worker/src/components/decoder_block.rs:13-32); this is the part that lets a block
+keep attention over recent keys beside a recurrent state.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..ops import kernels as K
+from .base import MIXERS, BuildContext, Mixer, ParamDecl, StepContext, StepIndex, register_mixer
+from .spec import PartSpec
+
+
+@register_mixer("parallel_mixers")
+class ParallelMixers(Mixer):
+    """params: left, right (PartSpec of a mixer each), left_scale, right_scale, left_prefix,
+    right_prefix (tensor-name prefixes inside this part, default "left." and "right.")."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.sides: List[Mixer] = [MIXERS.build(params["left"]), MIXERS.build(params["right"])]
+        self.scales = [float(params.get("left_scale", 1.0)), float(params.get("right_scale", 1.0))]
+        self.prefixes = [str(params.get("left_prefix", "left.")), str(params.get("right_prefix", "right."))]
+        self._needs = [m.cache_need() for m in self.sides]
+        if any(isinstance(n, (tuple, list)) for n in self._needs):
+            raise ValueError("a side of parallel_mixers is a single mixer, not another pair")
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(m.graph_safe for m in self.sides)
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {pre + name: d for pre, m in zip(self.prefixes, self.sides) for name, d in m.param_decls().items()}
+
+    def cache_need(self):
+        needs = tuple(n for n in self._needs if n is not None)
+        return needs or None
+
+    def step_indices(self) -> Sequence[StepIndex]:
+        return [need for m in self.sides for need in m.step_indices()]
+
+    def prepare(self, ctx: BuildContext) -> None:
+        super().prepare(ctx)
+        for m in self.sides:
+            m.prepare(ctx)
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for pre, m in zip(self.prefixes, self.sides):
+            m.load({name: tensors[pre + name] for name in m.param_decls() if pre + name in tensors})
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
+        caches = list(cache) if isinstance(cache, (tuple, list)) else [cache]
+        outs = []
+        for m, need in zip(self.sides, self._needs):
+            outs.append(m.forward(x, step, caches.pop(0) if need is not None else None))
+        out = torch.empty_like(outs[0])
+        K.scaled_sum(outs[0], outs[1], self.scales[0], self.scales[1], out)
+        return out

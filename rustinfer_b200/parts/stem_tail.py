@@ -41,6 +41,36 @@ class TokenEmbedding(Embedding):
         K.embed_gather(step.token_ids[: step.num_tokens], self.table, h)
 
 
+@register_embedding("sinusoid_embedding")
+class SinusoidEmbedding(TokenEmbedding):
+    """h[t, :] = E[ids[t], :] + s(p_t), with s(p)[2i] = sin(p * base^(-2i/hidden)) and s(p)[2i+1] the
+    cosine of the same angle.  params: vocab_size, hidden_size, base (default 10000), weight_name
+    (default "weight").  Frequencies are made in float64 on the host and the angle in float64 on
+    the device, so the vector is exact to fp32 rounding at every position."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.base = float(params.get("base", 10000.0))
+        self.weight_name = str(params.get("weight_name", "weight"))
+        self.freq: Optional[torch.Tensor] = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {self.weight_name: ParamDecl((self.vocab, self.hidden))}
+
+    def prepare(self, ctx) -> None:
+        super().prepare(ctx)
+        pairs = (self.hidden + 1) // 2
+        f = [self.base ** (-2.0 * i / self.hidden) for i in range(pairs)]
+        self.freq = torch.tensor(f, dtype=torch.float64).to(ctx.device)
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.table = tensors[self.weight_name].contiguous()
+
+    def forward(self, step: StepContext, h: torch.Tensor) -> None:
+        K.embed_sinusoid(step.token_ids[: step.num_tokens], step.positions[: step.num_tokens], self.table,
+                         self.freq, h)
+
+
 @register_head("linear_head")
 class LinearHead(Head):
     """params: vocab_size, hidden_size, tied (the configuration says the head is the embedding

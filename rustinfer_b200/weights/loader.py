@@ -43,8 +43,11 @@ def check_against(reader: SafetensorsReader, decls: Mapping[str, ParamDecl], fol
     have = set(n for n in reader.names() if not n.endswith(IGNORED_SUFFIXES))
     missing = sorted(n for n, d in decls.items() if n not in have and not d.optional)
     unexpected = sorted(have - set(decls))
+    def fits(got, want) -> bool:                 # a declared size of -1 is whatever the file has
+        return len(got) == len(want) and all(w == -1 or g == w for g, w in zip(got, want))
+
     wrong = [f"{n}: expected {list(decls[n].shape)}, got {list(reader.shape(n))}"
-             for n in sorted(have & set(decls)) if tuple(reader.shape(n)) != tuple(decls[n].shape)]
+             for n in sorted(have & set(decls)) if not fits(tuple(reader.shape(n)), tuple(decls[n].shape))]
     if missing or unexpected or wrong:
         raise WeightError(folder, missing, unexpected, wrong)
 

@@ -19,6 +19,7 @@ import torch
 from ..config.registry import resolve_architecture
 from .safetensors_io import write_safetensors
 
+FREE_SIZE = 16          # stands in for a declared size of -1 (one that only a file's tensors give)
 _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
 
 
@@ -41,12 +42,13 @@ def random_tensors(config: Mapping[str, Any], seed: int, std: float = 0.02, norm
         if d.optional:                   # a tied head is not stored
             continue
         g = _generator(seed, name)
-        if d.init == "ones":
-            t = torch.ones(d.shape, dtype=torch.float32)
+        shape = tuple(FREE_SIZE if n == -1 else n for n in d.shape)    # a size only the file would give
+        if d.init in ("ones", "zeros"):
+            t = torch.ones(shape, dtype=torch.float32) if d.init == "ones" else torch.zeros(shape, dtype=torch.float32)
             if norm_std > 0:
-                t += torch.randn(d.shape, generator=g, dtype=torch.float32) * norm_std
+                t += torch.randn(shape, generator=g, dtype=torch.float32) * norm_std
         else:
-            t = torch.randn(d.shape, generator=g, dtype=torch.float32) * std
+            t = torch.randn(shape, generator=g, dtype=torch.float32) * std
         out[name] = t.to(store)
     return out
 
