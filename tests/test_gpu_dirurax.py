@@ -1,0 +1,480 @@
+"""The Dirurax family on the GPU against the plain implementation: every kernel alone, then the
+engine under every way of cutting the work (whole prompts, a decoded tail, portions down to two
+tokens, mixed batches with pages and state slots used again), in true 32-bit and in bfloat16, on
+small configurations that differ in every size; greedy generation through `Engine`."""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_dirurax as P
+from dirurax_helpers import CONFIGS, Plain, config_json, make_sharp_model
+from helpers import random_ids, rel_err
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DEV = "cuda:0"
+F64 = torch.float64
+# max |engine - plain| / max |plain| over the compared logits; see tests/test_gpu_replay.py for how
+# such bounds are read.  fp32 sums a few hundred products per output against float64.
+TOL = {"float32": 3e-5, "bfloat16": 6e-2}
+DTYPES = ["float32", "bfloat16"]
+NAMES = sorted(CONFIGS)
+
+
+def K():
+    from rustinfer_b200.ops import kernels
+    return kernels
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float32) * scale
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+# =============================================================================== kernels alone
+def test_embed_sinusoid_far_positions():
+    V, d = 50, 37
+    table = rnd(V, d, seed=1).to(torch.bfloat16).to(DEV)
+    ids = [3, 49, 0, 7, 7]
+    pos = [0, 1, 999, 65537, 1000003]
+    freq = torch.tensor([10000.0 ** (-2.0 * i / d) for i in range((d + 1) // 2)], dtype=F64, device=DEV)
+    out = torch.empty((5, d), dtype=torch.float32, device=DEV)
+    K().embed_sinusoid(i32(ids), i32(pos), table, freq, out)
+    ref = table.cpu().to(F64)[ids] + P.sinusoid_positions(pos, d)
+    assert float((out.cpu().to(F64) - ref).abs().max()) < 1e-6       # fp32 rounding of the sum only
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sandwich_norm(dtype):
+    T, d, eps = 7, 83, 1e-3
+    h = rnd(T, d, seed=1, scale=3.0)
+    delta = (rnd(T, d, seed=2, scale=5.0) + 2.0).to(dtype)
+    ws = [rnd(d, seed=3 + i).to(dtype) for i in range(4)]
+    hd = h.to(DEV)
+    out = torch.empty((T, d), dtype=dtype, device=DEV)
+    K().sandwich_norm(hd, delta.to(DEV), ws[0].to(DEV), ws[1].to(DEV), ws[2].to(DEV), ws[3].to(DEV), out, eps)
+    w64 = [w.to(F64) for w in ws]
+    h_ref = h.to(F64) + P.layer_norm(delta.to(F64), w64[0], w64[1], eps)
+    assert float((hd.cpu().to(F64) - h_ref).abs().max()) < 2e-5
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert float((out.cpu().to(F64) - P.layer_norm(h_ref, w64[2], w64[3], eps)).abs().max()) < tol
+    # rows: only the named rows, the stream is not written, no bias
+    before = hd.clone()
+    rows = i32([5, 0])
+    out2 = torch.empty((2, d), dtype=dtype, device=DEV)
+    K().sandwich_norm(hd, delta.to(DEV), ws[0].to(DEV), None, ws[2].to(DEV), None, out2, eps, rows)
+    assert torch.equal(hd, before)
+    r2 = P.layer_norm(before.cpu().to(F64)[[5, 0]] + P.layer_norm(delta.to(F64)[[5, 0]], w64[0], None, eps), w64[2], None, eps)
+    assert float((out2.cpu().to(F64) - r2).abs().max()) < tol
+    # the add alone
+    K().sandwich_norm(hd, delta.to(DEV), ws[0].to(DEV), ws[1].to(DEV), None, None, None, eps)
+    assert float((hd.cpu().to(F64) - (before.cpu().to(F64) + P.layer_norm(delta.to(F64), w64[0], w64[1], eps))).abs().max()) < 2e-5
+
+
+def test_activations_and_scaled_sum():
+    x = rnd(1000, seed=4, scale=3.0).to(DEV)
+    for kind, fn in ((K().ACT_GELU_ERF, P.gelu_erf), (K().ACT_TANH, torch.tanh),
+                     (K().ACT_GELU_TANH, lambda z: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))))):
+        out = torch.empty_like(x)
+        K().activation(x, out, kind)
+        assert float((out.cpu().to(F64) - fn(x.cpu().to(F64))).abs().max()) < 1e-6
+    y = rnd(1000, seed=5).to(DEV)
+    out = torch.empty_like(x)
+    K().scaled_sum(x, y, 0.6, -1.7, out)
+    assert float((out.cpu().to(F64) - (0.6 * x.cpu().to(F64) - 1.7 * y.cpu().to(F64))).abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("per_head", [False, True])
+def test_gated_head_norm(per_head):
+    T, H, dv, eps = 6, 3, 20, 1e-4
+    o = rnd(T, H * dv, seed=1, scale=4.0)
+    buf = rnd(T, 2 * H * dv + 5, seed=2).to(torch.bfloat16)          # the gate is a column view
+    gate = buf[:, 5: 5 + H * dv]
+    w = rnd(H * dv if per_head else dv, seed=3).to(torch.bfloat16)
+    for act, fn in ((K().GATE_SILU, torch.nn.functional.silu), (K().GATE_SIGMOID, torch.sigmoid)):
+        out = torch.empty((T, H * dv), dtype=torch.bfloat16, device=DEV)
+        K().gated_head_norm(o.to(DEV), buf.to(DEV)[:, 5: 5 + H * dv], w.to(DEV), per_head, act, eps, out, H, dv)
+        n = P.rms_divide(o.to(F64).view(T, H, dv), eps)
+        n = n * (w.to(F64).view(H, dv) if per_head else w.to(F64))
+        ref = n.reshape(T, H * dv) * fn(gate.to(F64))
+        assert rel_err(out, ref) < 1e-2
+
+
+def paged(keys, vals, page, table, dtype):
+    """A cache [pages, Hkv*page*(dk+dv)] (or [pages, 2, Hkv, page, d] when the sizes are equal) that holds
+    keys [n, G, dk] and vals [n, G, dv] of one request in the pages `table` names; the rest is poison."""
+    n, G, dk = keys.shape
+    dv = vals.shape[2]
+    pages = max(table) + 2
+    c = torch.full((pages, G * page * (dk + dv)), 1e4, dtype=torch.float32)
+    for t in range(n):
+        pg, off = table[t // page], t % page
+        for g in range(G):
+            c[pg, (g * page + off) * dk: (g * page + off + 1) * dk] = keys[t, g]
+            b = G * page * dk + (g * page + off) * dv
+            c[pg, b: b + dv] = vals[t, g]
+    c = c.to(dtype).to(DEV)
+    return c.view(pages, 2, G, page, dk) if dk == dv else c
+
+
+@pytest.mark.parametrize("dk,dv", [(16, 24), (32, 32), (40, 8), (20, 36)])
+def test_block_attention_edges(dk, dv):
+    """One key stands out for every query (its score is 30 above the rest), so the output is that
+    key's value when the key is visible and something else when it is not.  Keys just inside and
+    just outside the block's edge, in prompt portions and for single tokens, with the block's edge
+    inside a page, at a page's edge and the pages in a scrambled order."""
+    page, block, H, G, n = 8, 20, 4, 2, 75
+    table = [7, 2, 9, 0, 5, 3, 8, 1, 6, 4]
+    unit = torch.nn.functional.normalize(rnd(n, dk, seed=2), dim=-1)
+    cos = unit @ unit.T - 2.0 * torch.eye(n)
+    gain = 30.0 / (1.0 - float(cos.max()))                            # the looked-for key leads by 30
+    keys = unit[:, None, :].repeat(1, G, 1)
+    vals = rnd(n, G, dv, seed=1)
+    cache = paged(keys, vals, page, table, torch.float32)
+    bt = i32([table])
+
+    def attend(first, count, targets):
+        """Queries at positions first..first+count-1; query i looks for key targets[i]."""
+        q = torch.zeros(count, H * dk)
+        for i, tgt in enumerate(targets):
+            q[i].view(H, dk)[:] = keys[tgt, 0] * gain
+        out = torch.empty((count, H * dv), dtype=torch.float32, device=DEV)
+        tiles = list(range(0, count, 16))
+        K().attention_plain(q.to(DEV), out, cache, bt, i32([0, count]), i32([first + count]), i32([0] * len(tiles)),
+                            i32(tiles), H, G, dk, 1.0, None, block, dv)
+        return out.cpu().view(count, H, dv)
+
+    def check(pos, tgt, out_row):
+        seen = tgt <= pos and tgt // block == pos // block
+        for h in range(H):
+            close = float((out_row[h] - vals[tgt, h // (H // G)]).abs().max()) < 1e-3
+            assert close == seen, (pos, tgt, h)
+
+    # a prompt portion that starts inside a block and crosses two edges
+    first, count = 13, 50
+    for shift in (0, 1, 2, 19, 20, 21):
+        targets = [max(0, p - shift) for p in range(first, first + count)]
+        out = attend(first, count, targets)
+        for i, p in enumerate(range(first, first + count)):
+            check(p, targets[i], out[i])
+    # single tokens at and around the edges, looking at the first and last key of the block and beyond it
+    for p in (19, 20, 21, 39, 40, 41, 59, 60, 74):
+        for tgt in {p, p // block * block, max(0, p // block * block - 1), max(0, p - 19), max(0, p - 20)}:
+            check(p, tgt, attend(p, 1, [tgt])[0])
+
+
+def test_head_norm_scatter():
+    T, Hq, G, dk, dv, page, eps = 9, 4, 2, 12, 20, 4, 1e-3
+    width = Hq * dk + G * (dk + dv)
+    qkv = rnd(T, width, seed=1, scale=2.0)
+    qw, kw = rnd(dk, seed=2), rnd(dk, seed=3)
+    slots = [13, 2, -1, 7, 0, 22, 5, 9, 10]
+    cache = torch.full((6, G * page * (dk + dv)), 77.0, device=DEV)
+    x = qkv.clone().to(DEV)
+    K().head_norm_scatter(x, qw.to(DEV), kw.to(DEV), True, eps, i32(slots), cache, Hq, G, dk, dv)
+    q64 = qkv.to(F64)
+    qn = P.rms_divide(q64[:, : Hq * dk].view(T, Hq, dk), eps) * qw.to(F64)
+    kn = P.rms_divide(q64[:, Hq * dk: (Hq + G) * dk].view(T, G, dk), eps) * kw.to(F64)
+    vn = P.rms_divide(q64[:, (Hq + G) * dk:].view(T, G, dv), eps)
+    assert float((x.cpu().to(F64)[:, : Hq * dk] - qn.reshape(T, -1)).abs().max()) < 1e-5
+    assert torch.equal(x.cpu()[:, Hq * dk:], qkv[:, Hq * dk:])                    # k and v stay in the buffer
+    c = cache.cpu().to(F64)
+    written = torch.zeros_like(c, dtype=torch.bool)
+    for t, s in enumerate(slots):
+        if s < 0:
+            continue
+        pg, off = s // page, s % page
+        for g in range(G):
+            a = (g * page + off) * dk
+            assert float((c[pg, a: a + dk] - kn[t, g]).abs().max()) < 1e-5
+            written[pg, a: a + dk] = True
+            b = G * page * dk + (g * page + off) * dv
+            assert float((c[pg, b: b + dv] - vn[t, g]).abs().max()) < 1e-5
+            written[pg, b: b + dv] = True
+    assert bool((c[~written] == 77.0).all())
+
+
+def _scan_pieces(T, cuts):
+    at, out = 0, []
+    for c in cuts:
+        out.append((at, at + c))
+        at += c
+    assert at == T
+    return out
+
+
+@pytest.mark.parametrize("dk,dv,H", [(8, 40, 2), (24, 24, 3), (100, 9, 1), (64, 64, 2), (76, 76, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_scan_kernel(dk, dv, H, dtype):
+    """Two requests walked in pieces of changing size (one token, two, many), side by side in one
+    launch where their pieces meet, their states in slots 3 and 1 of a state tensor whose other
+    rows must stay as they were."""
+    T, tau = 45, 4.0
+    buf = [rnd(T, 2 * H * dk + H * dv + 3, seed=s).to(dtype) for s in (1, 2)]     # q, k, v as column views
+    z = [rnd(T, H * dk, seed=s, scale=2.0) for s in (3, 4)]
+    bias = rnd(H * dk, seed=5).to(dtype)
+    state = torch.full((5, H, dk, dv), 9.0, device=DEV)
+    state[3] = 0
+    state[1] = 0
+    cuts = [_scan_pieces(T, [1, 2, 17, 1, 8, 16]), _scan_pieces(T, [20, 1, 1, 3, 9, 11])]
+    outs = [torch.zeros(T, H * dv), torch.zeros(T, H * dv)]
+    for (a0, a1), (b0, b1) in zip(*cuts):
+        q = torch.cat([buf[0][a0:a1], buf[1][b0:b1]]).to(DEV)
+        zz = torch.cat([z[0][a0:a1], z[1][b0:b1]]).to(DEV)
+        n = q.shape[0]
+        o = torch.empty((n, H * dv), dtype=torch.float32, device=DEV)
+        K().gated_scan(q[:, 3: 3 + H * dk], q[:, 3 + H * dk: 3 + 2 * H * dk], q[:, 3 + 2 * H * dk:], zz, bias.to(DEV),
+                       dk ** -0.5, tau, o, state, i32([0, a1 - a0, n]), i32([3, 1]), 2, H, dk, dv)
+        outs[0][a0:a1] = o[: a1 - a0].cpu()
+        outs[1][b0:b1] = o[a1 - a0:].cpu()
+    for r in range(2):
+        b64 = buf[r].to(F64)
+        q = (b64[:, 3: 3 + H * dk] * dk ** -0.5).view(T, H, dk)
+        k = b64[:, 3 + H * dk: 3 + 2 * H * dk].view(T, H, dk)
+        v = b64[:, 3 + 2 * H * dk:].view(T, H, dv)
+        alpha = torch.sigmoid(z[r].to(F64) + bias.to(F64)).pow(1 / tau).view(T, H, dk)
+        assert rel_err(outs[r], P.gla_scan(q, k, v, alpha).reshape(T, -1)) < 2e-5
+    assert bool((state[[0, 2, 4]] == 9.0).all())
+
+
+@pytest.mark.parametrize("d,H", [(8, 2), (20, 3), (48, 2), (76, 1), (128, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_delta_scan_kernel(d, H, dtype):
+    T = 45
+    buf = [rnd(T, 4 * H * d + 1, seed=s).to(dtype) for s in (1, 2)]               # r, k, v, a as column views
+    zw = [rnd(T, H * d, seed=s, scale=2.0) for s in (3, 4)]
+    ab, wb = rnd(H * d, seed=5).to(dtype), rnd(H * d, seed=6).to(dtype)
+    rate = math.exp(-0.5)
+    state = torch.zeros((3, H, d, d), device=DEV)
+    cuts = [_scan_pieces(T, [1, 2, 17, 1, 8, 16]), _scan_pieces(T, [20, 1, 1, 3, 9, 11])]
+    outs = [torch.zeros(T, H * d), torch.zeros(T, H * d)]
+    for (a0, a1), (b0, b1) in zip(*cuts):
+        x = torch.cat([buf[0][a0:a1], buf[1][b0:b1]]).to(DEV)
+        zz = torch.cat([zw[0][a0:a1], zw[1][b0:b1]]).to(DEV)
+        n, w = x.shape[0], H * d
+        o = torch.empty((n, w), dtype=torch.float32, device=DEV)
+        K().delta_scan(x[:, 1: 1 + w], x[:, 1 + w: 1 + 2 * w], x[:, 1 + 2 * w: 1 + 3 * w], x[:, 1 + 3 * w:], ab.to(DEV),
+                       zz, wb.to(DEV), rate, 1e-6, o, state, i32([0, a1 - a0, n]), i32([2, 0]), 2, H, d, d)
+        outs[0][a0:a1] = o[: a1 - a0].cpu()
+        outs[1][b0:b1] = o[a1 - a0:].cpu()
+    for r in range(2):
+        b64 = buf[r].to(F64)
+        w = H * d
+        rr, k, v = (b64[:, 1 + i * w: 1 + (i + 1) * w].view(T, H, d) for i in range(3))
+        a = torch.sigmoid(b64[:, 1 + 3 * w:] + ab.to(F64)).view(T, H, d)
+        decay = torch.exp(-rate * torch.sigmoid(zw[r].to(F64) + wb.to(F64))).view(T, H, d)
+        assert rel_err(outs[r], P.delta_scan(rr, k, v, decay, a).reshape(T, -1)) < 2e-5
+    assert bool((state[1] == 0).all())
+
+
+def test_gated_scan_keeps_a_far_key():
+    """With decays of one, keys along the axes and a query along one axis, the output is the sum of
+    the values written along that axis however long ago: 600 tokens in portions, read by a single token."""
+    dk, dv, T = 16, 8, 600
+    k = torch.zeros(T + 1, dk)
+    for t in range(T):
+        k[t, t % dk] = 1.0
+    k[T] = 0
+    v = rnd(T + 1, dv, seed=1)
+    q = torch.zeros(T + 1, dk)
+    q[T, 5] = 1.0
+    z = torch.full((T + 1, dk), 40.0)                                  # sigmoid(40)^(1/tau) = 1 in fp32
+    state = torch.zeros((1, 1, dk, dv), device=DEV)
+    at = 0
+    for n in (64, 2, 300, 1, 233, 1):
+        o = torch.empty((n, dv), dtype=torch.float32, device=DEV)
+        K().gated_scan(q[at: at + n].to(DEV), k[at: at + n].to(DEV), v[at: at + n].to(DEV), z[at: at + n].to(DEV), None,
+                       1.0, 7.0, o, state, i32([0, n]), i32([0]), 1, 1, dk, dv)
+        at += n
+    want = v[5:T:dk].to(F64).sum(0)
+    assert float((o[-1].cpu().to(F64) - want).abs().max()) < 1e-4
+
+
+# ============================================================================ the engine
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("dirurax")
+    out = {}
+    for n in NAMES:
+        folder = make_sharp_model(str(root / n), n, seed=21 + ord(n))
+        out[n] = (folder, Plain(folder))
+    return out
+
+
+def runner(folder, dtype, max_tokens=512, page=16, seqs=4, pages=None, capture=None):
+    from rustinfer_b200.engine.runner import ModelRunner
+    return ModelRunner(folder, dtype=dtype, max_model_len=max_tokens, page_size=page,
+                       num_pages=pages if pages is not None else max_tokens // page,
+                       max_batch_seqs=seqs, max_batch_tokens=max_tokens, capture_sizes=capture)
+
+
+def run_cuts(r, rid, ids, cuts):
+    from rustinfer_b200.engine.runner import StepEntry
+    r.open(rid)
+    outs, at = [], 0
+    for c in cuts:
+        outs.append(r.step([StepEntry(rid, ids[at: at + c], list(range(c)))]))
+        at += c
+    assert at == len(ids)
+    r.close(rid)
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_tail_and_portions(models, name, dtype):
+    folder, plain = models[name]
+    V = CONFIGS[name]["vocab"]
+    r = runner(folder, dtype, page=8 if name == "Y" else 16)
+    for n, seed in [(130, 1), (61, 2), (1, 3), (3, 4)]:
+        ids = random_ids(n, V, seed)
+        ref = plain.logits(ids)
+        assert rel_err(run_cuts(r, "w", ids, [n]), ref) <= TOL[dtype]          # the first tokens included
+        if n < 40:
+            continue
+        tail = run_cuts(r, "t", ids, [n - 36] + [1] * 36)
+        assert rel_err(tail, ref) <= TOL[dtype]
+        cuts, left, sizes = [], n, [2, 7, 1, 16, 2, 33, 24, 5, 2, 64]
+        while left:
+            c = min(sizes[len(cuts) % len(sizes)], left)
+            cuts.append(c)
+            left -= c
+        assert rel_err(run_cuts(r, "p", ids, cuts), ref) <= TOL[dtype]
+        assert rel_err(run_cuts(r, "two", ids[:40], [2] * 20), ref[:40]) <= TOL[dtype]
+    r.cache.check_invariants()
+    torch.cuda.synchronize()
+    r.check_kernel_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_mixed_batches_reuse_pages_and_slots(models, name, dtype):
+    """Three state slots and a pool that holds far less than the requests' sum: requests come and go,
+    portions of prompts run beside single tokens, and every request's logits are those it has alone."""
+    from rustinfer_b200.engine.runner import StepEntry
+    folder, plain = models[name]
+    V = CONFIGS[name]["vocab"]
+    r = runner(folder, dtype, max_tokens=256, page=16, seqs=3, pages=14)
+    lens = {"a": 150, "b": 37, "c": 90, "d": 2, "e": 120, "f": 64}
+    ids = {k: random_ids(n, V, 100 + i) for i, (k, n) in enumerate(lens.items())}
+    at = {k: 0 for k in ids}
+    got = {k: [] for k in ids}
+    waiting = list(ids)
+    live = []
+    portion = {"a": [33, 1, 1, 50, 2], "b": [5, 1, 1], "c": [64, 1, 25], "d": [1], "e": [2, 100, 1], "f": [16, 47, 1]}
+    turn = 0
+    while waiting or live:
+        while waiting and len(live) < 3:
+            k = waiting.pop(0)
+            r.open(k)
+            live.append(k)
+        entries = []
+        for k in live:
+            if (turn + ord(k)) % 4 == 3 and len(live) > 1 and len(entries) + 1 < len(live):
+                continue                                         # a request sits a step out now and then
+            plan = portion[k]
+            n = min(plan[min(len(got[k]), len(plan) - 1)], lens[k] - at[k])
+            entries.append(StepEntry(k, ids[k][at[k]: at[k] + n], list(range(n))))
+        if not entries:
+            turn += 1
+            continue
+        lg = r.step(entries)
+        row = 0
+        for e in entries:
+            n = len(e.tokens)
+            got[e.request_id].append(lg[row: row + n])
+            row += n
+            at[e.request_id] += n
+            if at[e.request_id] == lens[e.request_id]:
+                r.close(e.request_id)
+                live.remove(e.request_id)
+        r.cache.check_invariants()
+        turn += 1
+    for k in ids:
+        assert rel_err(torch.cat(got[k]), plain.logits(ids[k])) <= TOL[dtype], k
+    torch.cuda.synchronize()
+    r.check_kernel_errors()
+
+
+def test_fp32_logits_do_not_depend_on_the_cut(models):
+    """The recurrences, the attention and the products sum in an order that the cut does not change."""
+    folder, _ = models["X"]
+    r = runner(folder, "float32")
+    ids = random_ids(90, CONFIGS["X"]["vocab"], 9)
+    whole = run_cuts(r, "w", ids, [90])
+    assert torch.equal(run_cuts(r, "p", ids, [31, 2, 1, 24, 32]), whole)
+    assert torch.equal(run_cuts(r, "t", ids, [60] + [1] * 30), whole)
+
+
+@pytest.mark.parametrize("name", ["X", "Z"])
+def test_long_decoding_and_graphs(models, name):
+    """300 single tokens after a short prompt, eager and from captured steps: blocks of positions
+    pass, their pages are given back, and the logits stay those of the plain model."""
+    from rustinfer_b200.engine.runner import StepEntry
+    folder, plain = models[name]
+    ids = random_ids(310, CONFIGS[name]["vocab"], 5)
+    ref = plain.logits(ids)
+    for capture in (None, [1, 2]):
+        r = runner(folder, "float32", max_tokens=320, page=16, seqs=2, pages=8 if name == "X" else 20, capture=capture)
+        r.open("a")
+        out = [r.step([StepEntry("a", ids[:10], list(range(10)))])]
+        for t in range(10, 310):
+            out.append(r.step([StepEntry("a", ids[t: t + 1], [0])]))
+        assert rel_err(torch.cat(out), ref) <= TOL["float32"]
+        if capture:
+            assert r.graph_replays == 300
+        r.close("a")
+        r.cache.check_invariants()
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_engine(models, name):
+    """`Engine.generate`: scheduler, chunked prefill, continuous batching, device argmax, decode graphs."""
+    from rustinfer_b200.engine.engine import Engine
+    from rustinfer_b200.sampling.params import SamplingParams
+    folder, plain = models[name]
+    V = CONFIGS[name]["vocab"]
+    prompts = [random_ids(n, V, 50 + n) for n in (45, 3, 70, 1, 26)]
+    want = [plain.greedy(p, 12) for p in prompts]
+    eng = Engine(folder, dtype="float32", max_batch_seqs=3, max_model_len=128, paged_block_size=16,
+                 num_blocks=24, max_batch_tokens=64, chunked_prefill_size=32)
+    got = [res.tokens for res in eng.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))]
+    assert got == want
+    eng16 = Engine(folder, dtype="bfloat16", max_batch_seqs=3, max_model_len=128, paged_block_size=16,
+                   num_blocks=24, max_batch_tokens=64, chunked_prefill_size=32)
+    got16 = [res.tokens for res in eng16.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))]
+    same = sum(a == b for g, w in zip(got16, want) for a, b in zip(g, w))
+    assert same >= 0.6 * 12 * len(prompts), (got16, want)
+
+
+def test_trace_replay_command(models, tmp_path):
+    folder, plain = models["Y"]
+    V = CONFIGS["Y"]["vocab"]
+    a, b = random_ids(70, V, 1), random_ids(20, V, 2)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:33], "want": [0, 32]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[33:69], "want": []}, {"id": "b", "tokens": b[:19], "want": [18]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[19:], "want": [0]}, {"id": "a", "tokens": a[69:], "want": [0]}], "end": ["a", "b"]},
+    ]
+    out = tmp_path / "out"
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    import numpy as np
+    ra, rb = plain.logits(a), plain.logits(b)
+    g0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4")).view(2, V)
+    assert rel_err(g0, ra[[0, 32]]) <= TOL["float32"]
+    g1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4")).view(1, V)
+    assert rel_err(g1, rb[[18]]) <= TOL["float32"]
+    g2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4")).view(2, V)
+    assert rel_err(g2, torch.stack([rb[19], ra[69]])) <= TOL["float32"]
