@@ -8,8 +8,8 @@
 //
 // The columns of S do not mix, so a CTA owns a tile of value channels of one head of one batch
 // entry and walks the entry's tokens in order, whatever their number: a prompt, a portion of
-// one or a single decoded token.  A column is held by R lanes of a warp, each with DK/R of its
-// rows in registers for the whole walk; sums over key channels are a fixed tree of shuffles,
+// one or a single decoded token.  A column is held by R lanes of a warp, each with DK/R consecutive
+// rows in registers for the whole walk; sums over key channels are a fixed tree of adds and shuffles,
 // so a token's result has the same bits however the tokens were cut into steps or batches.
 // Per round of TC tokens the CTA stages the vectors every column needs (decays, gates, unit
 // keys: each formed once, in fp32) in shared memory.  Projections arrive in the activation
@@ -24,10 +24,17 @@ namespace {
 constexpr int DK = RI_KDIM;
 static_assert(DK >= 1 && DK <= 512, "key size up to 512");
 constexpr int R = DK <= 64 ? 4 : 8;             // lanes that share a column
-constexpr int NR = (DK + R - 1) / R;            // rows of the column each of them holds
+constexpr int NR = ((DK + R - 1) / R + 3) / 4 * 4;   // rows of the column each of them holds (a multiple of 4)
+// A lane's rows are consecutive (row i belongs to lane i / NR) and lie NRP floats from the next
+// lane's in shared memory: NRP = 4 mod 8, so the 16-byte loads of the lanes of a group fall into
+// different banks.  Rows beyond DK are staged as zeros and need no guard.
+constexpr int NRP = NR % 8 == 4 ? NR : NR + 4;
+constexpr int ROWLEN = R * NRP;
 constexpr int THREADS = 128;
 constexpr int COLS = THREADS / R;               // value channels per CTA
 constexpr int TC = DK > 256 ? 4 : 8;            // tokens staged per round
+
+__device__ __forceinline__ int row_at(int i) { return (i / NR) * NRP + (i % NR); }
 
 __device__ __forceinline__ float group_sum(float v) {
 #pragma unroll
@@ -51,7 +58,8 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
                   int H, int dv) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float qs[TC][DK], ks[TC][DK], as[TC][DK], vs[TC][COLS];
+    __shared__ __align__(16) float qs[TC][ROWLEN], ks[TC][ROWLEN], as[TC][ROWLEN];
+    __shared__ float vs[TC][COLS];
     const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
     const int tid = threadIdx.x, col = tid / R, rg = tid % R;
     const int t_begin = cu_q[b], t_end = cu_q[b + 1];
@@ -61,45 +69,58 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
     float S[NR];
 #pragma unroll
     for (int n = 0; n < NR; ++n) {
-        const int i = rg + R * n;
+        const int i = rg * NR + n;
         S[n] = (col_ok && i < DK) ? sp[(size_t)i * dv] : 0.f;
     }
+    for (int e = tid; e < TC * ROWLEN; e += THREADS)       // rows beyond DK and the gaps stay zero
+        (&qs[0][0])[e] = (&ks[0][0])[e] = (&as[0][0])[e] = 0.f;
     for (int t0 = t_begin; t0 < t_end; t0 += TC) {
         const int nt = min(TC, t_end - t0);
         __syncthreads();
         for (int e = tid; e < nt * DK; e += THREADS) {
             const int tok = e / DK, i = e - tok * DK;
             const size_t t = (size_t)(t0 + tok);
-            qs[tok][i] = ld(q, t * q_stride + (size_t)h * DK + i) * q_scale;
-            ks[tok][i] = ld(k, t * k_stride + (size_t)h * DK + i);
+            const int at = row_at(i);
+            qs[tok][at] = ld(q, t * q_stride + (size_t)h * DK + i) * q_scale;
+            ks[tok][at] = ld(k, t * k_stride + (size_t)h * DK + i);
             float zz = z[t * z_stride + (size_t)h * DK + i];
             if (z_bias) zz += to_f32<TW>(z_bias[(size_t)h * DK + i]);
-            as[tok][i] = expf(log_sigmoid_f(zz) * inv_tau);
+            as[tok][at] = expf(log_sigmoid_f(zz) * inv_tau);
         }
         for (int e = tid; e < nt * COLS; e += THREADS) {
             const int tok = e / COLS, c = e - tok * COLS;
             vs[tok][c] = c0 + c < dv ? ld(v, (size_t)(t0 + tok) * v_stride + (size_t)h * dv + c0 + c) : 0.f;
         }
         __syncthreads();
-        for (int tok = 0; tok < nt; ++tok) {
-            const float vj = vs[tok][col];
-            float o = 0.f;
 #pragma unroll
-            for (int n = 0; n < NR; ++n) {
-                const int i = rg + R * n;
-                if (DK % R == 0 || i < DK) {
-                    S[n] = fmaf(as[tok][i], S[n], ks[tok][i] * vj);
-                    o = fmaf(S[n], qs[tok][i], o);
+        for (int tok = 0; tok < TC; ++tok) {
+            if (tok < nt) {
+                const float vj = vs[tok][col];
+                const float4* a4 = reinterpret_cast<const float4*>(&as[tok][rg * NRP]);
+                const float4* k4 = reinterpret_cast<const float4*>(&ks[tok][rg * NRP]);
+                const float4* q4 = reinterpret_cast<const float4*>(&qs[tok][rg * NRP]);
+                float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+                for (int m = 0; m < NR / 4; ++m) {
+                    const float4 a = a4[m], kk = k4[m], qq = q4[m];
+                    S[4 * m + 0] = fmaf(a.x, S[4 * m + 0], kk.x * vj);
+                    S[4 * m + 1] = fmaf(a.y, S[4 * m + 1], kk.y * vj);
+                    S[4 * m + 2] = fmaf(a.z, S[4 * m + 2], kk.z * vj);
+                    S[4 * m + 3] = fmaf(a.w, S[4 * m + 3], kk.w * vj);
+                    o0 = fmaf(S[4 * m + 0], qq.x, o0);
+                    o1 = fmaf(S[4 * m + 1], qq.y, o1);
+                    o0 = fmaf(S[4 * m + 2], qq.z, o0);
+                    o1 = fmaf(S[4 * m + 3], qq.w, o1);
                 }
+                const float o = group_sum(o0 + o1);
+                if (rg == 0 && col_ok) out[((size_t)(t0 + tok) * H + h) * dv + c0 + col] = o;
             }
-            o = group_sum(o);
-            if (rg == 0 && col_ok) out[((size_t)(t0 + tok) * H + h) * dv + c0 + col] = o;
         }
     }
     if (col_ok) {
 #pragma unroll
         for (int n = 0; n < NR; ++n) {
-            const int i = rg + R * n;
+            const int i = rg * NR + n;
             if (i < DK) sp[(size_t)i * dv] = S[n];
         }
     }
@@ -116,7 +137,8 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
                   int H, int dv) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float rs[TC][DK], ks[TC][DK], ws[TC][DK], us[TC][DK], aus[TC][DK], vs[TC][COLS];
+    __shared__ __align__(16) float rs[TC][ROWLEN], ks[TC][ROWLEN], ws[TC][ROWLEN], us[TC][ROWLEN], aus[TC][ROWLEN];
+    __shared__ float vs[TC][COLS];
     const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
     const int tid = threadIdx.x, col = tid / R, rg = tid % R;
     const int lane = tid & 31, warp = tid >> 5;
@@ -127,9 +149,11 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
     float S[NR];
 #pragma unroll
     for (int n = 0; n < NR; ++n) {
-        const int i = rg + R * n;
+        const int i = rg * NR + n;
         S[n] = (col_ok && i < DK) ? sp[(size_t)i * dv] : 0.f;
     }
+    for (int e = tid; e < TC * ROWLEN; e += THREADS)       // rows beyond DK and the gaps stay zero
+        (&rs[0][0])[e] = (&ks[0][0])[e] = (&ws[0][0])[e] = (&us[0][0])[e] = (&aus[0][0])[e] = 0.f;
     for (int t0 = t_begin; t0 < t_end; t0 += TC) {
         const int nt = min(TC, t_end - t0);
         __syncthreads();
@@ -137,14 +161,15 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
             const int tok = e / DK, i = e - tok * DK;
             const size_t t = (size_t)(t0 + tok);
             const size_t c = (size_t)h * DK + i;
-            rs[tok][i] = ld(r, t * r_stride + c);
-            ks[tok][i] = ld(k, t * k_stride + c);
+            const int at = row_at(i);
+            rs[tok][at] = ld(r, t * r_stride + c);
+            ks[tok][at] = ld(k, t * k_stride + c);
             float zz = zw[t * zw_stride + c];
             if (zw_bias) zz += to_f32<TW>(zw_bias[c]);
-            ws[tok][i] = expf(-decay_rate * sigmoid_f(zz));
+            ws[tok][at] = expf(-decay_rate * sigmoid_f(zz));
             float az = ld(za, t * za_stride + c);
             if (za_bias) az += to_f32<TW>(za_bias[c]);
-            aus[tok][i] = sigmoid_f(az);                      // times the unit key below
+            aus[tok][at] = sigmoid_f(az);                     // times the unit key below
         }
         for (int e = tid; e < nt * COLS; e += THREADS) {
             const int tok = e / COLS, c = e - tok * COLS;
@@ -153,42 +178,61 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
         __syncthreads();
         for (int tok = warp; tok < nt; tok += THREADS / 32) {  // unit keys: a warp a token
             float ss = 0.f;
-            for (int i = lane; i < DK; i += 32) ss = fmaf(ks[tok][i], ks[tok][i], ss);
+            for (int i = lane; i < DK; i += 32) {
+                const float x = ks[tok][row_at(i)];
+                ss = fmaf(x, x, ss);
+            }
             ss = warp_sum(ss);
             const float inv = 1.0f / sqrtf(ss + unit_eps);
             for (int i = lane; i < DK; i += 32) {
-                const float u = ks[tok][i] * inv;
-                us[tok][i] = u;
-                aus[tok][i] *= u;
+                const int at = row_at(i);
+                const float u = ks[tok][at] * inv;
+                us[tok][at] = u;
+                aus[tok][at] *= u;
             }
         }
         __syncthreads();
-        for (int tok = 0; tok < nt; ++tok) {
-            const float vj = vs[tok][col];
-            float dot = 0.f;
 #pragma unroll
-            for (int n = 0; n < NR; ++n) {
-                const int i = rg + R * n;
-                if (DK % R == 0 || i < DK) dot = fmaf(us[tok][i], S[n], dot);
-            }
-            dot = group_sum(dot);
-            float o = 0.f;
+        for (int tok = 0; tok < TC; ++tok) {
+            if (tok < nt) {
+                const float vj = vs[tok][col];
+                const float4* u4 = reinterpret_cast<const float4*>(&us[tok][rg * NRP]);
+                float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-            for (int n = 0; n < NR; ++n) {
-                const int i = rg + R * n;
-                if (DK % R == 0 || i < DK) {
-                    S[n] = fmaf(ws[tok][i], S[n], fmaf(-aus[tok][i], dot, ks[tok][i] * vj));
-                    o = fmaf(S[n], rs[tok][i], o);
+                for (int m = 0; m < NR / 4; ++m) {
+                    const float4 u = u4[m];
+                    d0 = fmaf(u.x, S[4 * m + 0], d0);
+                    d1 = fmaf(u.y, S[4 * m + 1], d1);
+                    d0 = fmaf(u.z, S[4 * m + 2], d0);
+                    d1 = fmaf(u.w, S[4 * m + 3], d1);
                 }
+                const float dot = group_sum(d0 + d1);
+                const float4* w4 = reinterpret_cast<const float4*>(&ws[tok][rg * NRP]);
+                const float4* au4 = reinterpret_cast<const float4*>(&aus[tok][rg * NRP]);
+                const float4* k4 = reinterpret_cast<const float4*>(&ks[tok][rg * NRP]);
+                const float4* r4 = reinterpret_cast<const float4*>(&rs[tok][rg * NRP]);
+                float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+                for (int m = 0; m < NR / 4; ++m) {
+                    const float4 w = w4[m], au = au4[m], kk = k4[m], rr = r4[m];
+                    S[4 * m + 0] = fmaf(w.x, S[4 * m + 0], fmaf(-au.x, dot, kk.x * vj));
+                    S[4 * m + 1] = fmaf(w.y, S[4 * m + 1], fmaf(-au.y, dot, kk.y * vj));
+                    S[4 * m + 2] = fmaf(w.z, S[4 * m + 2], fmaf(-au.z, dot, kk.z * vj));
+                    S[4 * m + 3] = fmaf(w.w, S[4 * m + 3], fmaf(-au.w, dot, kk.w * vj));
+                    o0 = fmaf(S[4 * m + 0], rr.x, o0);
+                    o1 = fmaf(S[4 * m + 1], rr.y, o1);
+                    o0 = fmaf(S[4 * m + 2], rr.z, o0);
+                    o1 = fmaf(S[4 * m + 3], rr.w, o1);
+                }
+                const float o = group_sum(o0 + o1);
+                if (rg == 0 && col_ok) out[((size_t)(t0 + tok) * H + h) * dv + c0 + col] = o;
             }
-            o = group_sum(o);
-            if (rg == 0 && col_ok) out[((size_t)(t0 + tok) * H + h) * dv + c0 + col] = o;
         }
     }
     if (col_ok) {
 #pragma unroll
         for (int n = 0; n < NR; ++n) {
-            const int i = rg + R * n;
+            const int i = rg * NR + n;
             if (i < DK) sp[(size_t)i * dv] = S[n];
         }
     }
