@@ -839,9 +839,9 @@ def test_kernels_refuse_what_they_cannot_do():
     k = K()
     with pytest.raises(KernelError, match="CUDA tensors"):
         k.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
-    with pytest.raises(KernelError, match="multiples of 16"):
+    with pytest.raises(KernelError, match="up to 512"):
         from rustinfer_b200.ops import library
-        library.attention_plain(24)
+        library.attention_plain(520)
     with pytest.raises(KernelError):
         k.gemm_f32(torch.zeros(2, 3, device=dev()), torch.zeros(4, 5, device=dev()), torch.zeros(2, 4, device=dev()))
     with pytest.raises(KernelError):
