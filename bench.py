@@ -465,6 +465,182 @@ def kernel_ratios():
     return out
 
 
+# ------------------------------------------------- the Dirurax family beside Llama at equal size
+def _dirurax(width, layers, ff, vocab, gla, attn, delta, block):
+    """`layers` layers, every fourth attention over blocks of `block` positions beside a delta rule,
+    the others gated linear attention; a dense feed-forward in each."""
+    gh, gd, gv = gla
+    ah, akv, ad, av = attn
+    dh, dd = delta
+    out = []
+    for i in range(layers):
+        mlp = {"ff": ff, "kind": "dense"}
+        if i % 4 == 3:
+            out.append({"type": "parallel", "mlp": mlp, "mixer": {
+                "left": {"heads": ah, "kv_heads": akv, "dim": ad, "vdim": av, "scale": ad ** -0.5, "mask": {"size": block}},
+                "right": {"heads": dh, "dim": dd}, "left_scale": 0.5, "right_scale": 0.5}})
+        else:
+            out.append({"type": "gla", "mlp": mlp, "mixer": {"heads": gh, "dim": gd, "vdim": gv, "tau": 16.0}})
+    return {"architecture": "Dirurax", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": out}
+
+
+def _llama_like(width, layers, ff, vocab, heads, kv_heads, head_dim):
+    return dict(_llama(layers, width, heads, kv_heads, head_dim, ff, 32.0, True), vocab_size=vocab)
+
+
+# width, layers, feed-forward width, vocabulary; Dirurax: gla (heads, key, value), attention (heads, kv heads,
+# key, value), delta rule (heads, size), block of positions; Llama at the same width, layers, ff, vocabulary
+FAMILY_SIZES = {
+    "w1024": dict(width=1024, layers=8, ff=4096, vocab=32768, gla=(4, 128, 256), attn=(16, 4, 64, 64),
+                  delta=(8, 128), block=512, llama=(16, 4, 64)),
+    "w2048": dict(width=2048, layers=8, ff=8192, vocab=32768, gla=(8, 128, 256), attn=(32, 8, 64, 64),
+                  delta=(16, 128), block=1024, llama=(32, 8, 64)),
+}
+
+
+def dirurax_kernels(hbm_gbs, size):
+    """The new family's kernels alone at one size, 2,048 tokens of one request and 64 single tokens:
+    microseconds, and what that is of the bytes they must move at the measured copy bandwidth (or, for
+    the walks over tokens, of the fp32 multiply-adds at the CUDA cores' rate)."""
+    import torch
+    from rustinfer_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    sz = FAMILY_SIZES[size]
+    d = sz["width"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)
+    out = {}
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    fma_per_s = sms * 128 * 1.9e9                            # fp32 multiply-adds a second on the CUDA cores
+    for tag, T, entries in (("prefill2048", 2048, 1), ("decode64", 64, 64)):
+        cu = i32([i * (T // entries) for i in range(entries + 1)])
+        slots = i32(list(range(entries)))
+        # gated linear attention
+        H, dk, dv = sz["gla"]
+        proj = bf(T, 2 * H * dk + 2 * H * dv)
+        z = torch.randn(T, H * dk, device=dev)
+        bias = bf(H * dk)
+        o = torch.empty(T, H * dv, device=dev)
+        state = torch.zeros(entries + 1, H, dv, K.recurrent_state_rows(dk), device=dev)
+        us = time_kernel(lambda: K.gated_scan(proj[:, :H * dk], proj[:, H * dk:2 * H * dk], proj[:, 2 * H * dk:2 * H * dk + H * dv],
+                                              z, bias, dk ** -0.5, 16.0, o, state, cu, slots, entries, H, dk, dv), flush=flush)
+        moved = T * (2 * H * dk * 2 + H * dv * 2 + H * dk * 4 + H * dv * 4) + 2 * entries * H * dk * dv * 4
+        out[f"gated_scan_{tag}"] = {"us": round(us, 1), "hbm_frac": round(moved / (us * 1e-6) / 1e9 / hbm_gbs, 4),
+                                    "fma_frac": round(2 * T * H * dk * dv / (us * 1e-6) / fma_per_s, 4)}
+        y = torch.empty(T, H * dv, device=dev, dtype=torch.bfloat16)
+        w = bf(dv)
+        us = time_kernel(lambda: K.gated_head_norm(o, proj[:, 2 * H * dk + H * dv:], w, False, K.GATE_SILU, 1e-6, y, H, dv), flush=flush)
+        out[f"gated_head_norm_{tag}"] = {"us": round(us, 1), "hbm_frac": round(T * H * dv * 8 / (us * 1e-6) / 1e9 / hbm_gbs, 4)}
+        # delta rule
+        H, dk = sz["delta"]
+        proj = bf(T, 5 * H * dk)
+        zw = torch.randn(T, H * dk, device=dev)
+        b1, b2 = bf(H * dk), bf(H * dk)
+        o = torch.empty(T, H * dk, device=dev)
+        state = torch.zeros(entries + 1, H, dk, K.recurrent_state_rows(dk), device=dev)
+        us = time_kernel(lambda: K.delta_scan(proj[:, :H * dk], proj[:, H * dk:2 * H * dk], proj[:, 2 * H * dk:3 * H * dk],
+                                              proj[:, 4 * H * dk:], b1, zw, b2, 0.6065306597, 1e-6, o, state, cu, slots,
+                                              entries, H, dk, dk), flush=flush)
+        moved = T * (4 * H * dk * 2 + 2 * H * dk * 4) + 2 * entries * H * dk * dk * 4
+        out[f"delta_scan_{tag}"] = {"us": round(us, 1), "hbm_frac": round(moved / (us * 1e-6) / 1e9 / hbm_gbs, 4),
+                                    "fma_frac": round(3 * T * H * dk * dk / (us * 1e-6) / fma_per_s, 4)}
+        # layer norm around a sublayer beside the fused add + RMSNorm of the Llama blocks
+        h = torch.randn(T, d, device=dev)
+        delta = bf(T, d)
+        ws = [bf(d) for _ in range(4)]
+        xo = torch.empty(T, d, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.sandwich_norm(h, delta, ws[0], ws[1], ws[2], ws[3], xo, 1e-6), flush=flush)
+        us_rms = time_kernel(lambda: K.add_rmsnorm(h, delta, ws[0], 1e-6, xo), flush=flush)
+        moved = T * d * (4 + 4 + 2 + 2)
+        out[f"sandwich_norm_{tag}"] = {"us": round(us, 1), "hbm_frac": round(moved / (us * 1e-6) / 1e9 / hbm_gbs, 4),
+                                       "add_rmsnorm_us": round(us_rms, 1),
+                                       "add_rmsnorm_hbm_frac": round(moved / (us_rms * 1e-6) / 1e9 / hbm_gbs, 4)}
+    # attention over the current block of positions (fp32 arithmetic) beside the tcgen05 causal attention
+    # of the Llama blocks on the same heads, 2,048 tokens of one request
+    Hq, Hkv, hd, vd = sz["attn"]
+    T, page, block = 2048, PAGE, sz["block"]
+    pages = T // page
+    cache = bf(pages, 2, Hkv, page, hd)
+    table = i32([list(range(pages))])
+    q = bf(T, Hq * hd)
+    ao = torch.empty(T, Hq * vd, device=dev, dtype=torch.bfloat16)
+    tiles = list(range(0, T, 16))
+    te, t0 = i32([0] * len(tiles)), i32(tiles)
+    cu, kv = i32([0, T]), i32([T])
+    us = time_kernel(lambda: K.attention_plain(q, ao, cache, table, cu, kv, te, t0, Hq, Hkv, hd, hd ** -0.5, None, block, vd),
+                     repeats=5, flush=flush)
+    pairs = sum(min(p % block, p) + 1 for p in range(T))     # (query, key) pairs inside the blocks
+    out["block_attention_prefill2048"] = {"us": round(us, 1), "tflops": round(2 * pairs * Hq * (hd + vd) / (us * 1e-6) / 1e12, 2)}
+    if K.tc_attention_supports(Hq, Hkv, hd, page):
+        rows = K.tc_tokens_per_tile(Hq, Hkv)
+        tl = list(range(0, T, rows))
+        te2, t02 = i32([0] * len(tl)), i32(tl)
+        us2 = time_kernel(lambda: K.attention_prefill_tc(q, ao, cache, table, cu, kv, te2, t02, Hq, Hkv, hd, hd ** -0.5, None),
+                          flush=flush)
+        out["block_attention_prefill2048"].update(
+            causal_tc_us=round(us2, 1), causal_tc_tflops=round(2 * (T * (T + 1) // 2) * Hq * 2 * hd / (us2 * 1e-6) / 1e12, 2))
+    return out
+
+
+def family_bench(args) -> int:
+    """`--family dirurax`: prefill and decode throughput of Dirurax models at a few sizes beside
+    Llama models of the same width, depth, feed-forward width and vocabulary (random weights), and the
+    family's own kernels alone.  One JSON line."""
+    import torch
+    from rustinfer_b200.engine.engine import Engine
+    from rustinfer_b200.weights.random_init import write_random_model
+    hbm_gbs, bf16_tflops, peak_kind = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+    say = lambda msg: print(f"[bench] {msg}", file=sys.stderr, flush=True)
+    ctx, tokens = min(args.context, 4096), max(2, min(args.prompt_tokens, 8192))
+    result = {"family": "dirurax", "dtype": "bf16", "data": "synthetic", "peaks": peak_kind, "points": {}, "kernels": {}}
+    sizes = [s for s in FAMILY_SIZES if not args.size or s in args.size.split(",")]
+    for size in sizes:
+        sz = FAMILY_SIZES[size]
+        configs = {
+            "dirurax": _dirurax(sz["width"], sz["layers"], sz["ff"], sz["vocab"], sz["gla"], sz["attn"], sz["delta"], sz["block"]),
+            "llama": _llama_like(sz["width"], sz["layers"], sz["ff"], sz["vocab"], *sz["llama"])}
+        point = {}
+        for fam, cfg in configs.items():
+            with tempfile.TemporaryDirectory(prefix="rustinfer_b200_bench_") as tmp:
+                folder = write_random_model(os.path.join(tmp, "model"), cfg, seed=SEED, std=STD)
+                weights = os.path.getsize(os.path.join(folder, "model.safetensors"))
+                seqs = max(args.batch, 1)
+                longest = max(ctx, tokens)
+                engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=seqs, max_model_len=longest,
+                                paged_block_size=PAGE, num_blocks=seqs * longest // PAGE + 64,
+                                capture_sizes=[1, 2, 4, 8, 16, 32, 64], ignore_eos=True)
+                ms_p, pw = prefill_timed(engine, sz["vocab"], tokens, repeats=3)
+                windows += pw
+                steps = max(args.steps, 32)
+                decode_device_timed(engine, args.batch, steps, args.warmup, sz["vocab"], 1, ctx)      # graphs captured: untimed
+                (ms_d, launches, w), _all = median_of(
+                    lambda: decode_device_timed(engine, args.batch, steps, args.warmup, sz["vocab"], 2, ctx), 3)
+                windows.append(w)
+                point[fam] = {"prefill_tokens_per_s": round(tokens / ms_p * 1e3), "prefill_ms": round(ms_p, 3),
+                              "decode_tokens_per_s": round(args.batch / ms_d * 1e3, 1), "decode_ms_per_step": round(ms_d, 4),
+                              "decode_launches_per_step": launches // steps, "weight_mb": round(weights / 1e6, 1),
+                              "decode_weight_hbm_frac": round(weights / (ms_d * 1e-3) / 1e9 / hbm_gbs, 4)}
+                say(f"{size} {fam}: prefill {tokens} tokens {ms_p:.3f} ms, decode b{args.batch} ctx{ctx} {ms_d:.4f} ms/step")
+                del engine
+                torch.cuda.empty_cache()
+        point["prefill_ratio"] = round(point["dirurax"]["prefill_tokens_per_s"] / point["llama"]["prefill_tokens_per_s"], 3)
+        point["decode_ratio"] = round(point["dirurax"]["decode_tokens_per_s"] / point["llama"]["decode_tokens_per_s"], 3)
+        result["points"][size] = point
+        result["kernels"][size] = dirurax_kernels(hbm_gbs, size)
+        say(f"{size} kernels: {result['kernels'][size]}")
+    clocks.stop()
+    result["config"] = {"batch": args.batch, "context": ctx, "prompt_tokens": tokens,
+                        "sizes": {s: {k: v for k, v in FAMILY_SIZES[s].items()} for s in sizes},
+                        "l2": "a 256 MB buffer is rewritten between timed kernel runs; model steps read weights larger than L2"}
+    result["clocks"] = clocks.summary(windows)
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -488,6 +664,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: length of the prompt, computed in one step (up to 8192)")
+    ap.add_argument("--family", default="llama", choices=["llama", "dirurax"],
+                    help="dirurax: that family's prefill and decode at a few sizes beside Llama models of equal size, "
+                         "and its kernels alone (one JSON line of its own; the default workload is unchanged)")
+    ap.add_argument("--size", default="", help="with --family dirurax: sizes to run, with commas (default: all)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: --gpus {args.gpus} is not supported by this engine")
@@ -499,6 +679,8 @@ def main() -> int:
         return 0
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 2)
+    if args.family == "dirurax":
+        return family_bench(args)
 
     import torch
     from rustinfer_b200.engine.engine import Engine

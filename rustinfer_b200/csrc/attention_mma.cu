@@ -112,12 +112,20 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
 }
 
 // ================================================================== prefill / ragged
+// `block` > 0: a query sees only keys from the start of its own block of that many positions
+// (counted from position 0 of the request), a lower bound like the window's.  PRECISE: the
+// softmax weights enter the product with the values as fp32 and not rounded to bf16: a weight is
+// cut into three bf16 pieces (8 + 8 + 8 bits of its significand, the sum is the weight itself)
+// and each piece is multiplied on the tensor cores with fp32 accumulation.  The scores are fp32
+// sums of exact products of bf16 q and k in both forms.
+template <bool PRECISE>
 __global__ void __launch_bounds__(THREADS)
 prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                const bf16* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
                const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                const int* __restrict__ tile_entry, const int* __restrict__ tile_tok0,
-               int Hq, int Hkv, int Gc, int chunks, int tpt, int page_size, float scale_log2, int window) {
+               int Hq, int Hkv, int Gc, int chunks, int tpt, int page_size, float scale_log2, int window,
+               int block) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -150,7 +158,8 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     }
 
     const int p_first = pos0 + tok0, p_last = p_first + ntok - 1;
-    const int lo_tile = window > 0 ? max(0, p_first - window + 1) : 0;
+    int lo_tile = window > 0 ? max(0, p_first - window + 1) : 0;
+    if (block > 0) lo_tile = max(lo_tile, (p_first / block) * block);
     const int t_begin = lo_tile / KT, t_end = p_last / KT + 1;
     const int* bt = block_table + (size_t)b * table_stride;
 
@@ -168,6 +177,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         ok_row[i] = jj < ntok && hh < nheads;
         p_row[i] = p_first + jj;
         lo_row[i] = window > 0 ? max(0, p_row[i] - window + 1) : 0;
+        if (block > 0) lo_row[i] = max(lo_row[i], (p_row[i] / block) * block);
     }
 
     const int p_warp_first = p_first + (warp * 16) / Gc;     // position of the warp's first row
@@ -212,7 +222,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         // tiles that reach past the warp's first row (the diagonal) or a window need masks.
         const int key0 = t * KT + (lane & 3) * 2;
         float mx[2] = {-INFINITY, -INFINITY};
-        if (window > 0 || t * KT + KT - 1 > p_warp_first) {
+        if (window > 0 || block > 0 || t * KT + KT - 1 > p_warp_first) {
 #pragma unroll
             for (int n = 0; n < KT / 8; ++n) {
 #pragma unroll
@@ -257,17 +267,29 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         }
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
-            unsigned pa[4];
-            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            unsigned pa[PRECISE ? 3 : 1][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float a = s[2 * kk + (j >> 1)][(j & 1) * 2], b = s[2 * kk + (j >> 1)][(j & 1) * 2 + 1];
+#pragma unroll
+                for (int piece = 0; piece < (PRECISE ? 3 : 1); ++piece) {
+                    const unsigned packed = pack_bf16(a, b);
+                    pa[piece][j] = packed;
+                    if (PRECISE) {                                // what the piece left out, exactly
+                        a -= __uint_as_float(packed << 16);
+                        b -= __uint_as_float(packed & 0xffff0000u);
+                    }
+                }
+            }
 #pragma unroll
             for (int np = 0; np < NT / 2; ++np) {
                 unsigned vf[4];
                 ldmatrix_x4_trans(vf, Vs + (kk * 16 + (lane & 15)) * ROW + np * 16 + (lane >> 4) * 8);
-                mma_bf16(o[2 * np], pa, vf[0], vf[1]);
-                mma_bf16(o[2 * np + 1], pa, vf[2], vf[3]);
+#pragma unroll
+                for (int piece = (PRECISE ? 2 : 0); piece >= 0; --piece) {      // the small pieces first
+                    mma_bf16(o[2 * np], pa[piece], vf[0], vf[1]);
+                    mma_bf16(o[2 * np + 1], pa[piece], vf[2], vf[3]);
+                }
             }
         }
         __syncthreads();                                      // all warps are done with this buffer
@@ -859,8 +881,11 @@ bool decode_tma_takes(int page_size) {
 int configure() {
     static int status = -1;
     if (status < 0) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)PREFILL_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)PREFILL_SMEM);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
 #if RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128
@@ -904,17 +929,23 @@ RI_API int ri_attention_prefill_bf16(const void* q, int q_stride, void* out, int
                                      const void* cache, const int* block_table, int table_stride,
                                      const int* cu_q, const int* kv_len, const int* tile_entry,
                                      const int* tile_tok0, int n_tiles, int Hq, int Hkv, int page_size,
-                                     float scale, int window, void* stream) {
+                                     float scale, int window, int block, int precise, void* stream) {
     if (n_tiles <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
     int st = configure();
     if (st != 0) return st;
     const int G = Hq / Hkv, Gc = G < MT ? G : MT, chunks = (G + Gc - 1) / Gc, tpt = MT / Gc;
     dim3 grid(n_tiles, Hkv * chunks);
-    RI_CHECKED(ri_launch(prefill_kernel, dim3(grid), dim3(THREADS), PREFILL_SMEM, (cudaStream_t)stream, 
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
-        cu_q, kv_len, tile_entry, tile_tok0, Hq, Hkv, Gc, chunks, tpt, page_size,
-        scale * 1.4426950408889634f, window));
+    if (precise)
+        RI_CHECKED(ri_launch(prefill_kernel<true>, dim3(grid), dim3(THREADS), PREFILL_SMEM, (cudaStream_t)stream,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
+            cu_q, kv_len, tile_entry, tile_tok0, Hq, Hkv, Gc, chunks, tpt, page_size,
+            scale * 1.4426950408889634f, window, block));
+    else
+        RI_CHECKED(ri_launch(prefill_kernel<false>, dim3(grid), dim3(THREADS), PREFILL_SMEM, (cudaStream_t)stream,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
+            cu_q, kv_len, tile_entry, tile_tok0, Hq, Hkv, Gc, chunks, tpt, page_size,
+            scale * 1.4426950408889634f, window, block));
     return ri_launch_status();
 }
 

@@ -8,12 +8,17 @@
 //
 // The columns of S do not mix, so a CTA owns a tile of value channels of one head of one batch
 // entry and walks the entry's tokens in order, whatever their number: a prompt, a portion of
-// one or a single decoded token.  A column is held by R lanes of a warp, each with DK/R consecutive
-// rows in registers for the whole walk; sums over key channels are a fixed tree of adds and shuffles,
-// so a token's result has the same bits however the tokens were cut into steps or batches.
-// Per round of TC tokens the CTA stages the vectors every column needs (decays, gates, unit
-// keys: each formed once, in fp32) in shared memory.  Projections arrive in the activation
-// dtype; the state, the decays and every sum are fp32.
+// one or a single decoded token.  Four warps compute: a column is held by R lanes of a warp, each
+// with NR consecutive rows in registers for the whole walk; sums over key channels are a fixed
+// tree of adds and shuffles, so a token's result has the same bits however the tokens were cut
+// into steps or batches.  Four more warps load: while a round of TC tokens is computed they fetch
+// the next round's vectors (all loads of a round in flight at once), form what every column needs
+// once (decays, gates, unit keys, in fp32) and lay it into the other half of shared memory.
+// Projections arrive in the activation dtype; the state, the decays and every sum are fp32.
+//
+// The state of one (slot, head) is stored value channel by value channel, [dv][DKP] with
+// DKP = R * NR >= DK rows (the rows beyond DK stay zero), so that a lane's rows are 16-byte
+// vectors and a warp reads and writes whole lines.
 #include "common.cuh"
 
 #ifndef RI_KDIM
@@ -25,14 +30,19 @@ constexpr int DK = RI_KDIM;
 static_assert(DK >= 1 && DK <= 512, "key size up to 512");
 constexpr int R = DK <= 64 ? 4 : 8;             // lanes that share a column
 constexpr int NR = ((DK + R - 1) / R + 3) / 4 * 4;   // rows of the column each of them holds (a multiple of 4)
+constexpr int DKP = R * NR;                     // rows of a stored column
 // A lane's rows are consecutive (row i belongs to lane i / NR) and lie NRP floats from the next
 // lane's in shared memory: NRP = 4 mod 8, so the 16-byte loads of the lanes of a group fall into
-// different banks.  Rows beyond DK are staged as zeros and need no guard.
+// different banks.  Rows beyond DK are zeros there and need no guard.
 constexpr int NRP = NR % 8 == 4 ? NR : NR + 4;
 constexpr int ROWLEN = R * NRP;
-constexpr int THREADS = 128;
-constexpr int COLS = THREADS / R;               // value channels per CTA
-constexpr int TC = DK > 256 ? 4 : 8;            // tokens staged per round
+constexpr int WORKERS = 128;                    // threads that compute; as many load
+constexpr int THREADS = 2 * WORKERS;
+constexpr int COLS = WORKERS / R;               // value channels per CTA
+constexpr int TC = DK <= 128 ? 16 : DK <= 256 ? 8 : 4;    // tokens per round
+constexpr int PER = (TC * DK + WORKERS - 1) / WORKERS;    // elements of a vector a loading thread stages per round
+
+constexpr int half_floats(int arrays) { return arrays * TC * ROWLEN + TC * COLS; }
 
 __device__ __forceinline__ int row_at(int i) { return (i / NR) * NRP + (i % NR); }
 
@@ -43,14 +53,64 @@ __device__ __forceinline__ float group_sum(float v) {
 }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ void loaders_sync() { asm volatile("bar.sync 1, %0;" ::"n"(WORKERS) : "memory"); }
 
 template <typename T>
 __device__ __forceinline__ float ld(const T* p, size_t i) { return to_f32<T>(p[i]); }
 
+__device__ __forceinline__ void load_state(float (&S)[NR], const float* sp, bool ok) {
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m) {
+        const float4 x = ok ? reinterpret_cast<const float4*>(sp)[m] : make_float4(0.f, 0.f, 0.f, 0.f);
+        S[4 * m] = x.x; S[4 * m + 1] = x.y; S[4 * m + 2] = x.z; S[4 * m + 3] = x.w;
+    }
+}
+__device__ __forceinline__ void store_state(const float (&S)[NR], float* sp) {
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m)
+        reinterpret_cast<float4*>(sp)[m] = make_float4(S[4 * m], S[4 * m + 1], S[4 * m + 2], S[4 * m + 3]);
+}
+
+template <typename TA>
+__device__ __forceinline__ void stage_values(float* vs, const TA* v, int v_stride, int t0, int nt, int h, int dv,
+                                             int c0, int lt) {
+    for (int e = lt; e < nt * COLS; e += WORKERS) {
+        const int tok = e / COLS, c = e - tok * COLS;
+        vs[tok * COLS + c] = c0 + c < dv ? ld(v, (size_t)(t0 + tok) * v_stride + (size_t)h * dv + c0 + c) : 0.f;
+    }
+}
+
+// ------------------------------------------------------------------------------- gated
+struct GatedHalf {
+    float *q, *k, *a, *v;
+    __device__ GatedHalf(float* base) : q(base), k(base + TC * ROWLEN), a(base + 2 * TC * ROWLEN), v(base + 3 * TC * ROWLEN) {}
+};
+
+__device__ __forceinline__ float gated_token(float (&S)[NR], const GatedHalf& b, int tok, int rg, int col) {
+    const float vj = b.v[tok * COLS + col];
+    const float4* a4 = reinterpret_cast<const float4*>(b.a + tok * ROWLEN + rg * NRP);
+    const float4* k4 = reinterpret_cast<const float4*>(b.k + tok * ROWLEN + rg * NRP);
+    const float4* q4 = reinterpret_cast<const float4*>(b.q + tok * ROWLEN + rg * NRP);
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m) {
+        const float4 a = a4[m], kk = k4[m], qq = q4[m];
+        S[4 * m + 0] = fmaf(a.x, S[4 * m + 0], kk.x * vj);
+        S[4 * m + 1] = fmaf(a.y, S[4 * m + 1], kk.y * vj);
+        S[4 * m + 2] = fmaf(a.z, S[4 * m + 2], kk.z * vj);
+        S[4 * m + 3] = fmaf(a.w, S[4 * m + 3], kk.w * vj);
+        o0 = fmaf(S[4 * m + 0], qq.x, o0);
+        o1 = fmaf(S[4 * m + 1], qq.y, o1);
+        o0 = fmaf(S[4 * m + 2], qq.z, o0);
+        o1 = fmaf(S[4 * m + 3], qq.w, o1);
+    }
+    return group_sum(o0 + o1);
+}
+
 // q, k: [T, >= H*DK] with row strides; v: [T, >= H*dv]; z: fp32 logits of the decay [T, H*DK]
-// (+ z_bias [H*DK] when given); out: fp32 [T, H*dv]; state: [slots][H][DK][dv] fp32.
+// (+ z_bias [H*DK] when given); out: fp32 [T, H*dv]; state: [slots][H][dv][DKP] fp32.
 template <typename TA, typename TW>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, DK <= 128 ? 2 : 1)
 gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__ k, int k_stride,
                   const TA* __restrict__ v, int v_stride, const float* __restrict__ z, int z_stride,
                   const TW* __restrict__ z_bias, float q_scale, float inv_tau, float* __restrict__ out,
@@ -58,77 +118,128 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
                   int H, int dv) {
     pdl_trigger();
     pdl_wait();
-    __shared__ __align__(16) float qs[TC][ROWLEN], ks[TC][ROWLEN], as[TC][ROWLEN];
-    __shared__ float vs[TC][COLS];
+    extern __shared__ __align__(16) float smem[];
+    constexpr int HALF = half_floats(3);
     const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
-    const int tid = threadIdx.x, col = tid / R, rg = tid % R;
+    const int tid = threadIdx.x;
+    const bool loader = tid >= WORKERS;
+    const int lt = tid - WORKERS;
+    const int col = tid / R, rg = tid % R;                   // of the computing threads
     const int t_begin = cu_q[b], t_end = cu_q[b + 1];
-    const int slot = state_slots[b];
-    const bool col_ok = c0 + col < dv;
-    float* sp = state + (((size_t)slot * H + h) * DK) * dv + c0 + col;
-    float S[NR];
+    const int rounds = (t_end - t_begin + TC - 1) / TC;
+    for (int e = tid; e < 2 * HALF; e += THREADS) smem[e] = 0.f;     // rows beyond DK and the gaps stay zero
+    __syncthreads();
+
+    auto stage = [&](int round) {
+        const GatedHalf hb(smem + (round & 1) * HALF);
+        const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+        float qv[PER], kv[PER], zv[PER];
 #pragma unroll
-    for (int n = 0; n < NR; ++n) {
-        const int i = rg * NR + n;
-        S[n] = (col_ok && i < DK) ? sp[(size_t)i * dv] : 0.f;
-    }
-    for (int e = tid; e < TC * ROWLEN; e += THREADS)       // rows beyond DK and the gaps stay zero
-        (&qs[0][0])[e] = (&ks[0][0])[e] = (&as[0][0])[e] = 0.f;
-    for (int t0 = t_begin; t0 < t_end; t0 += TC) {
-        const int nt = min(TC, t_end - t0);
-        __syncthreads();
-        for (int e = tid; e < nt * DK; e += THREADS) {
-            const int tok = e / DK, i = e - tok * DK;
-            const size_t t = (size_t)(t0 + tok);
-            const int at = row_at(i);
-            qs[tok][at] = ld(q, t * q_stride + (size_t)h * DK + i) * q_scale;
-            ks[tok][at] = ld(k, t * k_stride + (size_t)h * DK + i);
-            float zz = z[t * z_stride + (size_t)h * DK + i];
-            if (z_bias) zz += to_f32<TW>(z_bias[(size_t)h * DK + i]);
-            as[tok][at] = expf(log_sigmoid_f(zz) * inv_tau);
-        }
-        for (int e = tid; e < nt * COLS; e += THREADS) {
-            const int tok = e / COLS, c = e - tok * COLS;
-            vs[tok][c] = c0 + c < dv ? ld(v, (size_t)(t0 + tok) * v_stride + (size_t)h * dv + c0 + c) : 0.f;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int tok = 0; tok < TC; ++tok) {
-            if (tok < nt) {
-                const float vj = vs[tok][col];
-                const float4* a4 = reinterpret_cast<const float4*>(&as[tok][rg * NRP]);
-                const float4* k4 = reinterpret_cast<const float4*>(&ks[tok][rg * NRP]);
-                const float4* q4 = reinterpret_cast<const float4*>(&qs[tok][rg * NRP]);
-                float o0 = 0.f, o1 = 0.f;
-#pragma unroll
-                for (int m = 0; m < NR / 4; ++m) {
-                    const float4 a = a4[m], kk = k4[m], qq = q4[m];
-                    S[4 * m + 0] = fmaf(a.x, S[4 * m + 0], kk.x * vj);
-                    S[4 * m + 1] = fmaf(a.y, S[4 * m + 1], kk.y * vj);
-                    S[4 * m + 2] = fmaf(a.z, S[4 * m + 2], kk.z * vj);
-                    S[4 * m + 3] = fmaf(a.w, S[4 * m + 3], kk.w * vj);
-                    o0 = fmaf(S[4 * m + 0], qq.x, o0);
-                    o1 = fmaf(S[4 * m + 1], qq.y, o1);
-                    o0 = fmaf(S[4 * m + 2], qq.z, o0);
-                    o1 = fmaf(S[4 * m + 3], qq.w, o1);
-                }
-                const float o = group_sum(o0 + o1);
-                if (rg == 0 && col_ok) out[((size_t)(t0 + tok) * H + h) * dv + c0 + col] = o;
+        for (int j = 0; j < PER; ++j) {
+            const int e = lt + j * WORKERS;
+            if (e < nt * DK) {
+                const int tok = e / DK, i = e - tok * DK;
+                const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
+                qv[j] = ld(q, t * q_stride + c);
+                kv[j] = ld(k, t * k_stride + c);
+                zv[j] = z[t * z_stride + c] + (z_bias ? to_f32<TW>(z_bias[c]) : 0.f);
             }
         }
-    }
-    if (col_ok) {
 #pragma unroll
-        for (int n = 0; n < NR; ++n) {
-            const int i = rg * NR + n;
-            if (i < DK) sp[(size_t)i * dv] = S[n];
+        for (int j = 0; j < PER; ++j) {
+            const int e = lt + j * WORKERS;
+            if (e < nt * DK) {
+                const int tok = e / DK, i = e - tok * DK;
+                const int at = tok * ROWLEN + row_at(i);
+                hb.q[at] = qv[j] * q_scale;
+                hb.k[at] = kv[j];
+                hb.a[at] = expf(log_sigmoid_f(zv[j]) * inv_tau);
+            }
         }
+        stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
+    };
+
+    const bool col_ok = !loader && c0 + col < dv;
+    float* sp = nullptr;
+    float S[NR];
+    if (loader) {
+        if (rounds > 0) stage(0);
+    } else {
+        sp = state + ((((size_t)state_slots[b] * H + h) * dv + c0 + col) * DKP + rg * NR);
+        load_state(S, sp, col_ok);
     }
+    __syncthreads();
+    for (int round = 0; round < rounds; ++round) {
+        if (loader) {
+            if (round + 1 < rounds) stage(round + 1);
+        } else {
+            const GatedHalf hb(smem + (round & 1) * HALF);
+            const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+            float* op = out + ((size_t)t0 * H + h) * dv + c0 + col;
+            if (nt == TC) {
+#pragma unroll 4
+                for (int tok = 0; tok < TC; ++tok) {
+                    const float o = gated_token(S, hb, tok, rg, col);
+                    if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
+                }
+            } else {
+#pragma unroll 1
+                for (int tok = 0; tok < nt; ++tok) {
+                    const float o = gated_token(S, hb, tok, rg, col);
+                    if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (col_ok) store_state(S, sp);
+}
+
+// ------------------------------------------------------------------------------- delta
+struct DeltaHalf {
+    float *r, *k, *w, *u, *au, *v;
+    __device__ DeltaHalf(float* base)
+        : r(base), k(base + TC * ROWLEN), w(base + 2 * TC * ROWLEN), u(base + 3 * TC * ROWLEN),
+          au(base + 4 * TC * ROWLEN), v(base + 5 * TC * ROWLEN) {}
+};
+
+__device__ __forceinline__ float delta_token(float (&S)[NR], const DeltaHalf& b, int tok, int rg, int col) {
+    const float vj = b.v[tok * COLS + col];
+    const int at = tok * ROWLEN + rg * NRP;
+    const float4* u4 = reinterpret_cast<const float4*>(b.u + at);
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m) {
+        const float4 u = u4[m];
+        d0 = fmaf(u.x, S[4 * m + 0], d0);
+        d1 = fmaf(u.y, S[4 * m + 1], d1);
+        d0 = fmaf(u.z, S[4 * m + 2], d0);
+        d1 = fmaf(u.w, S[4 * m + 3], d1);
+    }
+    const float dot = group_sum(d0 + d1);
+    const float4* w4 = reinterpret_cast<const float4*>(b.w + at);
+    const float4* au4 = reinterpret_cast<const float4*>(b.au + at);
+    const float4* k4 = reinterpret_cast<const float4*>(b.k + at);
+    const float4* r4 = reinterpret_cast<const float4*>(b.r + at);
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m) {
+        const float4 w = w4[m], au = au4[m], kk = k4[m], rr = r4[m];
+        S[4 * m + 0] = fmaf(w.x, S[4 * m + 0], fmaf(-au.x, dot, kk.x * vj));
+        S[4 * m + 1] = fmaf(w.y, S[4 * m + 1], fmaf(-au.y, dot, kk.y * vj));
+        S[4 * m + 2] = fmaf(w.z, S[4 * m + 2], fmaf(-au.z, dot, kk.z * vj));
+        S[4 * m + 3] = fmaf(w.w, S[4 * m + 3], fmaf(-au.w, dot, kk.w * vj));
+        o0 = fmaf(S[4 * m + 0], rr.x, o0);
+        o1 = fmaf(S[4 * m + 1], rr.y, o1);
+        o0 = fmaf(S[4 * m + 2], rr.z, o0);
+        o1 = fmaf(S[4 * m + 3], rr.w, o1);
+    }
+    return group_sum(o0 + o1);
 }
 
 // r, k, za: [T, >= H*DK]; v: [T, >= H*dv]; zw: fp32 logits of the decay [T, H*DK]; biases [H*DK] or null.
 template <typename TA, typename TW>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, DK <= 128 ? 2 : 1)
 delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__ k, int k_stride,
                   const TA* __restrict__ v, int v_stride, const TA* __restrict__ za, int za_stride,
                   const TW* __restrict__ za_bias, const float* __restrict__ zw, int zw_stride,
@@ -137,109 +248,111 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
                   int H, int dv) {
     pdl_trigger();
     pdl_wait();
-    __shared__ __align__(16) float rs[TC][ROWLEN], ks[TC][ROWLEN], ws[TC][ROWLEN], us[TC][ROWLEN], aus[TC][ROWLEN];
-    __shared__ float vs[TC][COLS];
+    extern __shared__ __align__(16) float smem[];
+    constexpr int HALF = half_floats(5);
     const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
-    const int tid = threadIdx.x, col = tid / R, rg = tid % R;
-    const int lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
+    const bool loader = tid >= WORKERS;
+    const int lt = tid - WORKERS;
+    const int col = tid / R, rg = tid % R;
     const int t_begin = cu_q[b], t_end = cu_q[b + 1];
-    const int slot = state_slots[b];
-    const bool col_ok = c0 + col < dv;
-    float* sp = state + (((size_t)slot * H + h) * DK) * dv + c0 + col;
-    float S[NR];
+    const int rounds = (t_end - t_begin + TC - 1) / TC;
+    for (int e = tid; e < 2 * HALF; e += THREADS) smem[e] = 0.f;
+    __syncthreads();
+
+    auto stage = [&](int round) {
+        const DeltaHalf hb(smem + (round & 1) * HALF);
+        const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+        float rv[PER], kv[PER], wv[PER], av[PER];
 #pragma unroll
-    for (int n = 0; n < NR; ++n) {
-        const int i = rg * NR + n;
-        S[n] = (col_ok && i < DK) ? sp[(size_t)i * dv] : 0.f;
-    }
-    for (int e = tid; e < TC * ROWLEN; e += THREADS)       // rows beyond DK and the gaps stay zero
-        (&rs[0][0])[e] = (&ks[0][0])[e] = (&ws[0][0])[e] = (&us[0][0])[e] = (&aus[0][0])[e] = 0.f;
-    for (int t0 = t_begin; t0 < t_end; t0 += TC) {
-        const int nt = min(TC, t_end - t0);
-        __syncthreads();
-        for (int e = tid; e < nt * DK; e += THREADS) {
-            const int tok = e / DK, i = e - tok * DK;
-            const size_t t = (size_t)(t0 + tok);
-            const size_t c = (size_t)h * DK + i;
-            const int at = row_at(i);
-            rs[tok][at] = ld(r, t * r_stride + c);
-            ks[tok][at] = ld(k, t * k_stride + c);
-            float zz = zw[t * zw_stride + c];
-            if (zw_bias) zz += to_f32<TW>(zw_bias[c]);
-            ws[tok][at] = expf(-decay_rate * sigmoid_f(zz));
-            float az = ld(za, t * za_stride + c);
-            if (za_bias) az += to_f32<TW>(za_bias[c]);
-            aus[tok][at] = sigmoid_f(az);                     // times the unit key below
+        for (int j = 0; j < PER; ++j) {
+            const int e = lt + j * WORKERS;
+            if (e < nt * DK) {
+                const int tok = e / DK, i = e - tok * DK;
+                const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
+                rv[j] = ld(r, t * r_stride + c);
+                kv[j] = ld(k, t * k_stride + c);
+                wv[j] = zw[t * zw_stride + c] + (zw_bias ? to_f32<TW>(zw_bias[c]) : 0.f);
+                av[j] = ld(za, t * za_stride + c) + (za_bias ? to_f32<TW>(za_bias[c]) : 0.f);
+            }
         }
-        for (int e = tid; e < nt * COLS; e += THREADS) {
-            const int tok = e / COLS, c = e - tok * COLS;
-            vs[tok][c] = c0 + c < dv ? ld(v, (size_t)(t0 + tok) * v_stride + (size_t)h * dv + c0 + c) : 0.f;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int e = lt + j * WORKERS;
+            if (e < nt * DK) {
+                const int tok = e / DK, i = e - tok * DK;
+                const int at = tok * ROWLEN + row_at(i);
+                hb.r[at] = rv[j];
+                hb.k[at] = kv[j];
+                hb.w[at] = expf(-decay_rate * sigmoid_f(wv[j]));
+                hb.au[at] = sigmoid_f(av[j]);                 // times the unit key below
+            }
         }
-        __syncthreads();
-        for (int tok = warp; tok < nt; tok += THREADS / 32) {  // unit keys: a warp a token
+        stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
+        loaders_sync();
+        const int lane = lt & 31;
+        for (int tok = lt >> 5; tok < nt; tok += WORKERS / 32) {      // unit keys: a warp a token
             float ss = 0.f;
             for (int i = lane; i < DK; i += 32) {
-                const float x = ks[tok][row_at(i)];
+                const float x = hb.k[tok * ROWLEN + row_at(i)];
                 ss = fmaf(x, x, ss);
             }
             ss = warp_sum(ss);
             const float inv = 1.0f / sqrtf(ss + unit_eps);
             for (int i = lane; i < DK; i += 32) {
-                const int at = row_at(i);
-                const float u = ks[tok][at] * inv;
-                us[tok][at] = u;
-                aus[tok][at] *= u;
+                const int at = tok * ROWLEN + row_at(i);
+                const float u = hb.k[at] * inv;
+                hb.u[at] = u;
+                hb.au[at] *= u;
+            }
+        }
+    };
+
+    const bool col_ok = !loader && c0 + col < dv;
+    float* sp = nullptr;
+    float S[NR];
+    if (loader) {
+        if (rounds > 0) stage(0);
+    } else {
+        sp = state + ((((size_t)state_slots[b] * H + h) * dv + c0 + col) * DKP + rg * NR);
+        load_state(S, sp, col_ok);
+    }
+    __syncthreads();
+    for (int round = 0; round < rounds; ++round) {
+        if (loader) {
+            if (round + 1 < rounds) stage(round + 1);
+        } else {
+            const DeltaHalf hb(smem + (round & 1) * HALF);
+            const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+            float* op = out + ((size_t)t0 * H + h) * dv + c0 + col;
+            if (nt == TC) {
+#pragma unroll 4
+                for (int tok = 0; tok < TC; ++tok) {
+                    const float o = delta_token(S, hb, tok, rg, col);
+                    if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
+                }
+            } else {
+#pragma unroll 1
+                for (int tok = 0; tok < nt; ++tok) {
+                    const float o = delta_token(S, hb, tok, rg, col);
+                    if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
+                }
             }
         }
         __syncthreads();
-#pragma unroll
-        for (int tok = 0; tok < TC; ++tok) {
-            if (tok < nt) {
-                const float vj = vs[tok][col];
-                const float4* u4 = reinterpret_cast<const float4*>(&us[tok][rg * NRP]);
-                float d0 = 0.f, d1 = 0.f;
-#pragma unroll
-                for (int m = 0; m < NR / 4; ++m) {
-                    const float4 u = u4[m];
-                    d0 = fmaf(u.x, S[4 * m + 0], d0);
-                    d1 = fmaf(u.y, S[4 * m + 1], d1);
-                    d0 = fmaf(u.z, S[4 * m + 2], d0);
-                    d1 = fmaf(u.w, S[4 * m + 3], d1);
-                }
-                const float dot = group_sum(d0 + d1);
-                const float4* w4 = reinterpret_cast<const float4*>(&ws[tok][rg * NRP]);
-                const float4* au4 = reinterpret_cast<const float4*>(&aus[tok][rg * NRP]);
-                const float4* k4 = reinterpret_cast<const float4*>(&ks[tok][rg * NRP]);
-                const float4* r4 = reinterpret_cast<const float4*>(&rs[tok][rg * NRP]);
-                float o0 = 0.f, o1 = 0.f;
-#pragma unroll
-                for (int m = 0; m < NR / 4; ++m) {
-                    const float4 w = w4[m], au = au4[m], kk = k4[m], rr = r4[m];
-                    S[4 * m + 0] = fmaf(w.x, S[4 * m + 0], fmaf(-au.x, dot, kk.x * vj));
-                    S[4 * m + 1] = fmaf(w.y, S[4 * m + 1], fmaf(-au.y, dot, kk.y * vj));
-                    S[4 * m + 2] = fmaf(w.z, S[4 * m + 2], fmaf(-au.z, dot, kk.z * vj));
-                    S[4 * m + 3] = fmaf(w.w, S[4 * m + 3], fmaf(-au.w, dot, kk.w * vj));
-                    o0 = fmaf(S[4 * m + 0], rr.x, o0);
-                    o1 = fmaf(S[4 * m + 1], rr.y, o1);
-                    o0 = fmaf(S[4 * m + 2], rr.z, o0);
-                    o1 = fmaf(S[4 * m + 3], rr.w, o1);
-                }
-                const float o = group_sum(o0 + o1);
-                if (rg == 0 && col_ok) out[((size_t)(t0 + tok) * H + h) * dv + c0 + col] = o;
-            }
-        }
     }
-    if (col_ok) {
-#pragma unroll
-        for (int n = 0; n < NR; ++n) {
-            const int i = rg * NR + n;
-            if (i < DK) sp[(size_t)i * dv] = S[n];
-        }
-    }
+    if (col_ok) store_state(S, sp);
+}
+
+template <typename Kernel>
+int allow_shared(Kernel kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return 0;
+    return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 }  // namespace
 
 RI_API int ri_recurrent_key_dim() { return DK; }
+RI_API int ri_recurrent_state_rows() { return DKP; }
 
 RI_API int ri_gated_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
                          const float* z, int z_stride, const void* z_bias, int act_dtype, int w_dtype,
@@ -248,9 +361,12 @@ RI_API int ri_gated_scan(const void* q, int q_stride, const void* k, int k_strid
     if (entries <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((dv + COLS - 1) / COLS, H, entries);
-#define RI_GS(TA, TW) RI_CHECKED(ri_launch(gated_scan_kernel<TA, TW>, grid, dim3(THREADS), 0, s, (const TA*)q, q_stride, \
+    const size_t smem = 2 * (size_t)half_floats(3) * sizeof(float);
+#define RI_GS(TA, TW) do { static bool allowed = false; \
+    if (!allowed) { RI_CHECKED(allow_shared(gated_scan_kernel<TA, TW>, smem)); allowed = true; } \
+    RI_CHECKED(ri_launch(gated_scan_kernel<TA, TW>, grid, dim3(THREADS), smem, s, (const TA*)q, q_stride, \
         (const TA*)k, k_stride, (const TA*)v, v_stride, z, z_stride, (const TW*)z_bias, q_scale, inv_tau, out, state, \
-        cu_q, state_slots, H, dv))
+        cu_q, state_slots, H, dv)); } while (0)
     if (act_dtype == RI_BF16 && w_dtype == RI_BF16) RI_GS(bf16, bf16);
     else if (act_dtype == RI_BF16) RI_GS(bf16, float);
     else if (w_dtype == RI_BF16) RI_GS(float, bf16);
@@ -267,9 +383,12 @@ RI_API int ri_delta_scan(const void* r, int r_stride, const void* k, int k_strid
     if (entries <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((dv + COLS - 1) / COLS, H, entries);
-#define RI_DS(TA, TW) RI_CHECKED(ri_launch(delta_scan_kernel<TA, TW>, grid, dim3(THREADS), 0, s, (const TA*)r, r_stride, \
+    const size_t smem = 2 * (size_t)half_floats(5) * sizeof(float);
+#define RI_DS(TA, TW) do { static bool allowed = false; \
+    if (!allowed) { RI_CHECKED(allow_shared(delta_scan_kernel<TA, TW>, smem)); allowed = true; } \
+    RI_CHECKED(ri_launch(delta_scan_kernel<TA, TW>, grid, dim3(THREADS), smem, s, (const TA*)r, r_stride, \
         (const TA*)k, k_stride, (const TA*)v, v_stride, (const TA*)za, za_stride, (const TW*)za_bias, zw, zw_stride, \
-        (const TW*)zw_bias, decay_rate, unit_eps, out, state, cu_q, state_slots, H, dv))
+        (const TW*)zw_bias, decay_rate, unit_eps, out, state, cu_q, state_slots, H, dv)); } while (0)
     if (act_dtype == RI_BF16 && w_dtype == RI_BF16) RI_DS(bf16, bf16);
     else if (act_dtype == RI_BF16) RI_DS(bf16, float);
     else if (w_dtype == RI_BF16) RI_DS(float, bf16);

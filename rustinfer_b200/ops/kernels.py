@@ -554,12 +554,30 @@ def scaled_sum(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torc
                                  stream_ptr()), "scaled_sum")
 
 
+_rows_checked = set()
+
+
+def recurrent_state_rows(key_dim: int) -> int:
+    """Rows a stored column of the recurrences' state has: the key size rounded up so that each of the
+    lanes that share a column (4 up to a key size of 64, 8 above) holds a multiple of 4 rows.  The
+    state of one request and head is [value_dim, rows] fp32; rows beyond key_dim stay zero."""
+    lanes = 4 if key_dim <= 64 else 8
+    per_lane = -(-(-(-key_dim // lanes)) // 4) * 4
+    return lanes * per_lane
+
+
 def _scan_common(state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor,
                  T: int, H: int, dk: int, dv: int, what: str) -> None:
     _i32(cu_q, "cu_q"); _i32(state_slots, "state_slots")
     _contig(state, "state"); _contig(out, "out")
-    if state.dtype != torch.float32 or state.dim() != 4 or tuple(state.shape[1:]) != (H, dk, dv):
-        raise KernelError(f"{what}: state is fp32 [slots, {H}, {dk}, {dv}]")
+    rows = recurrent_state_rows(dk)
+    if dk not in _rows_checked:                       # once per key size: host and kernel count alike
+        kept = int(L.recurrent(dk).ri_recurrent_state_rows())
+        if kept != rows:
+            raise KernelError(f"{what}: the kernel stores {kept} rows a column, the host counts {rows}")
+        _rows_checked.add(dk)
+    if state.dtype != torch.float32 or state.dim() != 4 or tuple(state.shape[1:]) != (H, dv, rows):
+        raise KernelError(f"{what}: state is fp32 [slots, {H}, {dv}, {rows}] (recurrent_state_rows({dk}) rows a column)")
     if out.dtype != torch.float32 or out.shape != (T, H * dv):
         raise KernelError(f"{what}: out is fp32 [T, H*dv]")
 
@@ -574,7 +592,7 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
                state_slots: torch.Tensor, entries: int, num_heads: int, key_dim: int, value_dim: int) -> None:
     """Gated linear attention over every entry's tokens in order, from and into state[slot]:
     S = diag(sigmoid(z + z_bias)^(1/tau)) S + k v^T, out = S^T (q * q_scale).  q, k [T, H*dk], v [T, H*dv]
-    (column views allowed), z fp32 [T, H*dk]."""
+    (column views allowed), z fp32 [T, H*dk]; state [slots, H, dv, recurrent_state_rows(dk)]."""
     require_cuda(q, k, v, z, z_bias, out, state, cu_q, state_slots)
     T, H, dk, dv = q.shape[0], num_heads, key_dim, value_dim
     _scan_common(state, out, cu_q, state_slots, T, H, dk, dv, "gated_scan")
@@ -635,8 +653,10 @@ def mma_tokens_per_tile(num_heads: int, num_kv_heads: int) -> int:
 
 def attention_prefill_bf16(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0,
                            num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                           window: Optional[int]) -> None:
-    """Tiles are (entry, first token) pairs of `mma_tokens_per_tile` tokens each."""
+                           window: Optional[int], block: Optional[int] = None, precise: bool = False) -> None:
+    """Tiles are (entry, first token) pairs of `mma_tokens_per_tile` tokens each.  `block`: a query
+    sees only the keys of its own block of that many positions.  `precise`: the softmax weights go
+    into the product with the values in full fp32 (as three bf16 pieces) instead of rounded to bf16."""
     _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim)
     require_cuda(tile_entry, tile_tok0)
     _i32(tile_entry, "tile_entry"); _i32(tile_tok0, "tile_tok0")
@@ -645,6 +665,7 @@ def attention_prefill_bf16(q, out, cache, block_table, cu_q, kv_len, tile_entry,
                                         block_table.stride(0), _p(cu_q), _p(kv_len), _p(tile_entry),
                                         _p(tile_tok0), tile_entry.numel(), num_heads, num_kv_heads,
                                         cache.shape[3], float(scale), int(window) if window else 0,
+                                        int(block) if block else 0, 1 if precise else 0,
                                         stream_ptr()), "attention_prefill_bf16")
 
 

@@ -29,7 +29,7 @@ _SIGNATURES = {
     "ri_decode_feedback": [_P, _P, _I, _P, _P, _I, _P, _P, _P],
     "ri_sample": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "ri_sample_by_sorting": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
-    "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _L, _P, _I, _P],
     "ri_attention_mma_tokens_per_tile": [_I],
     "ri_attention_prefill_tc": [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -112,7 +112,9 @@ def recurrent(key_dim: int) -> ctypes.CDLL:
     """The linear-attention recurrences (gated and delta rule) for one key size."""
     if not 1 <= key_dim <= 512:
         raise KernelError(f"the recurrence kernels take key sizes up to 512, got {key_dim}")
-    return _load(f"ri_recurrent_k{key_dim}", ["recurrent.cu"], [f"RI_KDIM={key_dim}"])
+    lib = _load(f"ri_recurrent_k{key_dim}", ["recurrent.cu"], [f"RI_KDIM={key_dim}"])
+    lib.ri_recurrent_state_rows.restype = _I
+    return lib
 
 
 def gemm_tc() -> ctypes.CDLL:

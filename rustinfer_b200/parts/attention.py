@@ -121,6 +121,19 @@ class GQAAttention(Mixer):
         else:
             self._single = None
             self._tiles = token_tiles(16, skip_single_token=False)
+        # a mixer with the further options in bfloat16, keys and values of one size the tensor-core
+        # kernel is built for: prompt portions run there with fp32 softmax weights (three bf16 pieces
+        # each), single tokens stay on the fp32-arithmetic kernel
+        self.precise_mma = (self.general and ctx.dtype == torch.bfloat16 and self.vd == self.hd
+                            and self.hd % 16 == 0 and 16 <= self.hd <= L.MMA_MAX_HEAD_DIM
+                            and os.environ.get("RUSTINFER_B200_BLOCK_ATTENTION", "mma") != "plain")
+        if self.precise_mma:
+            self._single = single_token_entries()
+            self._tiles = token_tiles(K.mma_tokens_per_tile(self.Hq, self.Hkv), skip_single_token=True)
+            key = ("zero_tile_starts", ctx.max_batch_seqs)
+            if key not in ctx.shared:
+                ctx.shared[key] = torch.zeros(ctx.max_batch_seqs + 4, dtype=torch.int32, device=ctx.device)
+            self._zeros = ctx.shared[key]
         if self.position_spec is not None:
             key = ("position", self.position_spec.key(), ctx.max_model_len)
             if key not in ctx.shared:
@@ -208,6 +221,18 @@ class GQAAttention(Mixer):
         g = step.groups[cache.group]
         if out is None:
             out = torch.empty((T, self.Hq * self.vd), dtype=self.ctx.dtype, device=q.device)
+        if self.precise_mma:
+            (single,) = step.index(self._single)
+            if single.numel():                        # every single token is a tile of one row
+                K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single,
+                                  self._zeros[: single.numel()], self.Hq, self.Hkv, self.hd, self.scale,
+                                  self.window, self.block, self.vd)
+            tile_entry, tile_tok0 = step.index(self._tiles)
+            if tile_entry.numel():
+                K.attention_prefill_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry,
+                                         tile_tok0, self.Hq, self.Hkv, self.hd, self.scale, self.window,
+                                         self.block, precise=True)
+            return out
         if not self.use_mma:
             tile_entry, tile_q0 = step.index(self._tiles)
             K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,

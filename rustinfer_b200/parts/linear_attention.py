@@ -51,7 +51,9 @@ class _StateMixer(Mixer):
         return self.tensor_names.get(local, local)
 
     def cache_need(self):
-        return FixedState((self.H, self.dk, self.dv), "float32")
+        # a request's state: per head and value channel the column of S over the key channels, padded
+        # to the rows the kernel keeps (the padding stays zero)
+        return FixedState((self.H, self.dv, K.recurrent_state_rows(self.dk)), "float32")
 
     def _widths(self) -> Dict[str, int]:
         raise NotImplementedError

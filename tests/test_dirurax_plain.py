@@ -156,7 +156,7 @@ def test_cache_layout_of_mixed_layers():
     assert kinds == [PagedKV, FixedState]
     need = lx.groups[lx.entry_cache[0][0][0]].need
     assert (need.head_dim, need.v_dim, need.block, need.window) == (16, 24, 24, None)
-    assert lx.groups[lx.entry_cache[0][1][0]].need.shape == (3, 20, 20)
+    assert lx.groups[lx.entry_cache[0][1][0]].need.shape == (3, 20, 32)      # 20 key channels kept as 4 lanes of 8
     assert len(lx.paged_groups()) == 1
     ly = layout("Y")
     assert len(ly.paged_groups()) == 2                 # two attentions of different sizes

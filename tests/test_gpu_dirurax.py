@@ -171,6 +171,46 @@ def test_block_attention_edges(dk, dv):
             check(p, tgt, attend(p, 1, [tgt])[0])
 
 
+@pytest.mark.parametrize("hd,H,G", [(32, 4, 2), (64, 6, 1)])
+def test_block_attention_on_tensor_cores(hd, H, G):
+    """Prompt portions of the bfloat16 engine: scores from the tensor cores, softmax weights kept in
+    fp32 (cut into three bf16 pieces for the product with the values), the block's lower bound.  Two
+    requests in one launch, one of them starting inside a block, against the plain model on the same
+    bf16 inputs; the only rounding left is that of the output."""
+    page, block = 16, 40
+    lens, firsts = [70, 33], [0, 27]                  # tokens of the portion, position of its first token
+    tables = [[3, 0, 5, 2, 7], [1, 4, 6, 8]]
+    pages = 10
+    cache = torch.full((pages, 2, G, page, hd), 1e4, dtype=torch.bfloat16)
+    qs, refs = [], []
+    for r, (n, first) in enumerate(zip(lens, firsts)):
+        total = first + n
+        k = rnd(total, G, hd, seed=10 + r).to(torch.bfloat16)
+        v = rnd(total, G, hd, seed=20 + r).to(torch.bfloat16)
+        q = rnd(total, H, hd, seed=30 + r, scale=2.0).to(torch.bfloat16)
+        for t in range(total):
+            cache[tables[r][t // page], 0, :, t % page] = k[t]
+            cache[tables[r][t // page], 1, :, t % page] = v[t]
+        refs.append(P.block_attention(q.to(F64), k.to(F64), v.to(F64), 0.3, block)[first:])
+        qs.append(q[first:].reshape(n, H * hd))
+    q = torch.cat(qs).to(DEV)
+    out = torch.empty_like(q)
+    rows = K().mma_tokens_per_tile(H, G)
+    te, t0 = [], []
+    for r, n in enumerate(lens):
+        for a in range(0, n, rows):
+            te.append(r)
+            t0.append(a)
+    bt = torch.zeros(2, 5, dtype=torch.int32)
+    for r in range(2):
+        bt[r, : len(tables[r])] = torch.tensor(tables[r])
+    K().attention_prefill_bf16(q, out, cache.to(DEV), bt.to(DEV), i32([0, lens[0], sum(lens)]),
+                               i32([f + n for f, n in zip(firsts, lens)]), i32(te), i32(t0), H, G, hd, 0.3, None,
+                               block=block, precise=True)
+    ref = torch.cat([x.reshape(x.shape[0], H * hd) for x in refs])
+    assert float((out.cpu().to(F64) - ref).abs().max()) <= 2.0 ** -8 * float(ref.abs().max()) * 1.01
+
+
 def test_head_norm_scatter():
     T, Hq, G, dk, dv, page, eps = 9, 4, 2, 12, 20, 4, 1e-3
     width = Hq * dk + G * (dk + dv)
@@ -221,7 +261,7 @@ def test_gated_scan_kernel(dk, dv, H, dtype):
     buf = [rnd(T, 2 * H * dk + H * dv + 3, seed=s).to(dtype) for s in (1, 2)]     # q, k, v as column views
     z = [rnd(T, H * dk, seed=s, scale=2.0) for s in (3, 4)]
     bias = rnd(H * dk, seed=5).to(dtype)
-    state = torch.full((5, H, dk, dv), 9.0, device=DEV)
+    state = torch.full((5, H, dv, K().recurrent_state_rows(dk)), 9.0, device=DEV)
     state[3] = 0
     state[1] = 0
     cuts = [_scan_pieces(T, [1, 2, 17, 1, 8, 16]), _scan_pieces(T, [20, 1, 1, 3, 9, 11])]
@@ -253,7 +293,7 @@ def test_delta_scan_kernel(d, H, dtype):
     zw = [rnd(T, H * d, seed=s, scale=2.0) for s in (3, 4)]
     ab, wb = rnd(H * d, seed=5).to(dtype), rnd(H * d, seed=6).to(dtype)
     rate = math.exp(-0.5)
-    state = torch.zeros((3, H, d, d), device=DEV)
+    state = torch.zeros((3, H, d, K().recurrent_state_rows(d)), device=DEV)
     cuts = [_scan_pieces(T, [1, 2, 17, 1, 8, 16]), _scan_pieces(T, [20, 1, 1, 3, 9, 11])]
     outs = [torch.zeros(T, H * d), torch.zeros(T, H * d)]
     for (a0, a1), (b0, b1) in zip(*cuts):
@@ -287,7 +327,7 @@ def test_gated_scan_keeps_a_far_key():
     q = torch.zeros(T + 1, dk)
     q[T, 5] = 1.0
     z = torch.full((T + 1, dk), 40.0)                                  # sigmoid(40)^(1/tau) = 1 in fp32
-    state = torch.zeros((1, 1, dk, dv), device=DEV)
+    state = torch.zeros((1, 1, dv, K().recurrent_state_rows(dk)), device=DEV)
     at = 0
     for n in (64, 2, 300, 1, 233, 1):
         o = torch.empty((n, dv), dtype=torch.float32, device=DEV)
