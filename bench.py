@@ -572,6 +572,15 @@ def dirurax_kernels(hbm_gbs, size):
                      repeats=5, flush=flush)
     pairs = sum(min(p % block, p) + 1 for p in range(T))     # (query, key) pairs inside the blocks
     out["block_attention_prefill2048"] = {"us": round(us, 1), "tflops": round(2 * pairs * Hq * (hd + vd) / (us * 1e-6) / 1e12, 2)}
+    if hd == vd and hd % 16 == 0:
+        rows = K.mma_tokens_per_tile(Hq, Hkv)
+        tl = list(range(0, T, rows))
+        te1, t01 = i32([0] * len(tl)), i32(tl)
+        us1 = time_kernel(lambda: K.attention_prefill_bf16(q, ao, cache, table, cu, kv, te1, t01, Hq, Hkv, hd, hd ** -0.5,
+                                                           None, block, precise=True), flush=flush)
+        out["block_attention_prefill2048"].update(
+            fp32_arithmetic_us=out["block_attention_prefill2048"]["us"], us=round(us1, 1),
+            tflops=round(2 * pairs * Hq * (hd + 3 * vd) / (us1 * 1e-6) / 1e12, 2))
     if K.tc_attention_supports(Hq, Hkv, hd, page):
         rows = K.tc_tokens_per_tile(Hq, Hkv)
         tl = list(range(0, T, rows))

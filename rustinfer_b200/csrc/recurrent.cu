@@ -2,9 +2,10 @@
 // kept in fp32 (compiled for one key size RI_KDIM; any value size):
 //
 //   gated      S_t = diag(alpha_t) S_{t-1} + k_t v_t^T                          o_t = S_t^T q_t
-//              alpha = sigmoid(z)^(1/tau), formed as exp(log_sigmoid(z) / tau)
 //   delta      S_t = diag(w_t) S_{t-1} - (a_t * u_t)(u_t^T S_{t-1}) + k_t v_t^T   o_t = S_t^T r_t
-//              u = k / sqrt(|k|^2 + unit_eps), w = exp(-decay_rate * sigmoid(z_w)), a = sigmoid(z_a)
+//
+// The decays alpha and w, the unit keys u and the products a * u arrive as fp32 vectors per token
+// (made from the projections by kernels that run over all tokens at once, sequence_parts.cu).
 //
 // The columns of S do not mix, so a CTA owns a tile of value channels of one head of one batch
 // entry and walks the entry's tokens in order, whatever their number: a prompt, a portion of
@@ -12,9 +13,9 @@
 // with NR consecutive rows in registers for the whole walk; sums over key channels are a fixed
 // tree of adds and shuffles, so a token's result has the same bits however the tokens were cut
 // into steps or batches.  Four more warps load: while a round of TC tokens is computed they fetch
-// the next round's vectors (all loads of a round in flight at once), form what every column needs
-// once (decays, gates, unit keys, in fp32) and lay it into the other half of shared memory.
-// Projections arrive in the activation dtype; the state, the decays and every sum are fp32.
+// the next round's vectors (all loads of a round in flight at once) and lay them into the other
+// half of shared memory.  Projections arrive in the activation dtype; the state, the decays and
+// every sum are fp32.
 //
 // The state of one (slot, head) is stored value channel by value channel, [dv][DKP] with
 // DKP = R * NR >= DK rows (the rows beyond DK stay zero), so that a lane's rows are 16-byte
@@ -51,9 +52,6 @@ __device__ __forceinline__ float group_sum(float v) {
     for (int o = 1; o < R; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
-__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
-__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
-__device__ __forceinline__ void loaders_sync() { asm volatile("bar.sync 1, %0;" ::"n"(WORKERS) : "memory"); }
 
 template <typename T>
 __device__ __forceinline__ float ld(const T* p, size_t i) { return to_f32<T>(p[i]); }
@@ -86,6 +84,8 @@ struct GatedHalf {
     __device__ GatedHalf(float* base) : q(base), k(base + TC * ROWLEN), a(base + 2 * TC * ROWLEN), v(base + 3 * TC * ROWLEN) {}
 };
 
+// One token for this lane's rows: the state update and the lane's part of the output's sum over key
+// channels (the parts of a group's lanes are added by group_sum).
 __device__ __forceinline__ float gated_token(float (&S)[NR], const GatedHalf& b, int tok, int rg, int col) {
     const float vj = b.v[tok * COLS + col];
     const float4* a4 = reinterpret_cast<const float4*>(b.a + tok * ROWLEN + rg * NRP);
@@ -104,16 +104,16 @@ __device__ __forceinline__ float gated_token(float (&S)[NR], const GatedHalf& b,
         o0 = fmaf(S[4 * m + 2], qq.z, o0);
         o1 = fmaf(S[4 * m + 3], qq.w, o1);
     }
-    return group_sum(o0 + o1);
+    return o0 + o1;
 }
 
-// q, k: [T, >= H*DK] with row strides; v: [T, >= H*dv]; z: fp32 logits of the decay [T, H*DK]
-// (+ z_bias [H*DK] when given); out: fp32 [T, H*dv]; state: [slots][H][dv][DKP] fp32.
-template <typename TA, typename TW>
+// q, k: [T, >= H*DK] with row strides; v: [T, >= H*dv]; alpha: fp32 decays [T, H*DK];
+// out: fp32 [T, H*dv]; state: [slots][H][dv][DKP] fp32.
+template <typename TA>
 __global__ void __launch_bounds__(THREADS, DK <= 128 ? 2 : 1)
 gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__ k, int k_stride,
-                  const TA* __restrict__ v, int v_stride, const float* __restrict__ z, int z_stride,
-                  const TW* __restrict__ z_bias, float q_scale, float inv_tau, float* __restrict__ out,
+                  const TA* __restrict__ v, int v_stride, const float* __restrict__ alpha, int a_stride,
+                  float q_scale, float* __restrict__ out,
                   float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                   int H, int dv) {
     pdl_trigger();
@@ -127,23 +127,25 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
     const int col = tid / R, rg = tid % R;                   // of the computing threads
     const int t_begin = cu_q[b], t_end = cu_q[b + 1];
     const int rounds = (t_end - t_begin + TC - 1) / TC;
-    for (int e = tid; e < 2 * HALF; e += THREADS) smem[e] = 0.f;     // rows beyond DK and the gaps stay zero
-    __syncthreads();
+    if (DKP != DK) {                                         // rows beyond DK stay zero
+        for (int e = tid; e < 2 * HALF; e += THREADS) smem[e] = 0.f;
+        __syncthreads();
+    }
 
     auto stage = [&](int round) {
         const GatedHalf hb(smem + (round & 1) * HALF);
         const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
-        float qv[PER], kv[PER], zv[PER];
+        // every load of the round is issued before the first is used: addresses past the round's
+        // end are clamped to its last element (read again, stored nowhere) so that no load is conditional
+        float qv[PER], kv[PER], av[PER];
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
-            const int e = lt + j * WORKERS;
-            if (e < nt * DK) {
-                const int tok = e / DK, i = e - tok * DK;
-                const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
-                qv[j] = ld(q, t * q_stride + c);
-                kv[j] = ld(k, t * k_stride + c);
-                zv[j] = z[t * z_stride + c] + (z_bias ? to_f32<TW>(z_bias[c]) : 0.f);
-            }
+            const int e = min(lt + j * WORKERS, nt * DK - 1);
+            const int tok = e / DK, i = e - tok * DK;
+            const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
+            qv[j] = ld(q, t * q_stride + c);
+            kv[j] = ld(k, t * k_stride + c);
+            av[j] = alpha[t * a_stride + c];
         }
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
@@ -153,7 +155,7 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
                 const int at = tok * ROWLEN + row_at(i);
                 hb.q[at] = qv[j] * q_scale;
                 hb.k[at] = kv[j];
-                hb.a[at] = expf(log_sigmoid_f(zv[j]) * inv_tau);
+                hb.a[at] = av[j];
             }
         }
         stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
@@ -177,15 +179,20 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
             const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
             float* op = out + ((size_t)t0 * H + h) * dv + c0 + col;
             if (nt == TC) {
-#pragma unroll 4
+                // the lanes' parts of a whole round first, their sums after: a shuffle orders the
+                // instructions around it, and sixteen in a row overlap where one a token would not
+                float part[TC];
+#pragma unroll
+                for (int tok = 0; tok < TC; ++tok) part[tok] = gated_token(S, hb, tok, rg, col);
+#pragma unroll
                 for (int tok = 0; tok < TC; ++tok) {
-                    const float o = gated_token(S, hb, tok, rg, col);
+                    const float o = group_sum(part[tok]);
                     if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
                 }
             } else {
 #pragma unroll 1
                 for (int tok = 0; tok < nt; ++tok) {
-                    const float o = gated_token(S, hb, tok, rg, col);
+                    const float o = group_sum(gated_token(S, hb, tok, rg, col));
                     if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
                 }
             }
@@ -234,16 +241,16 @@ __device__ __forceinline__ float delta_token(float (&S)[NR], const DeltaHalf& b,
         o0 = fmaf(S[4 * m + 2], rr.z, o0);
         o1 = fmaf(S[4 * m + 3], rr.w, o1);
     }
-    return group_sum(o0 + o1);
+    return o0 + o1;
 }
 
-// r, k, za: [T, >= H*DK]; v: [T, >= H*dv]; zw: fp32 logits of the decay [T, H*DK]; biases [H*DK] or null.
-template <typename TA, typename TW>
+// r, k: [T, >= H*DK]; v: [T, >= H*dv]; w (decays), u (unit keys), au (removal rate times unit key):
+// fp32 [T, H*DK] with one row stride.
+template <typename TA>
 __global__ void __launch_bounds__(THREADS, DK <= 128 ? 2 : 1)
 delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__ k, int k_stride,
-                  const TA* __restrict__ v, int v_stride, const TA* __restrict__ za, int za_stride,
-                  const TW* __restrict__ za_bias, const float* __restrict__ zw, int zw_stride,
-                  const TW* __restrict__ zw_bias, float decay_rate, float unit_eps, float* __restrict__ out,
+                  const TA* __restrict__ v, int v_stride, const float* __restrict__ w, const float* __restrict__ u,
+                  const float* __restrict__ au, int f_stride, float* __restrict__ out,
                   float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                   int H, int dv) {
     pdl_trigger();
@@ -257,24 +264,25 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
     const int col = tid / R, rg = tid % R;
     const int t_begin = cu_q[b], t_end = cu_q[b + 1];
     const int rounds = (t_end - t_begin + TC - 1) / TC;
-    for (int e = tid; e < 2 * HALF; e += THREADS) smem[e] = 0.f;
-    __syncthreads();
+    if (DKP != DK) {
+        for (int e = tid; e < 2 * HALF; e += THREADS) smem[e] = 0.f;
+        __syncthreads();
+    }
 
     auto stage = [&](int round) {
         const DeltaHalf hb(smem + (round & 1) * HALF);
         const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
-        float rv[PER], kv[PER], wv[PER], av[PER];
+        float rv[PER], kv[PER], wv[PER], uv[PER], av[PER];      // loads unconditional, as in the gated kernel
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
-            const int e = lt + j * WORKERS;
-            if (e < nt * DK) {
-                const int tok = e / DK, i = e - tok * DK;
-                const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
-                rv[j] = ld(r, t * r_stride + c);
-                kv[j] = ld(k, t * k_stride + c);
-                wv[j] = zw[t * zw_stride + c] + (zw_bias ? to_f32<TW>(zw_bias[c]) : 0.f);
-                av[j] = ld(za, t * za_stride + c) + (za_bias ? to_f32<TW>(za_bias[c]) : 0.f);
-            }
+            const int e = min(lt + j * WORKERS, nt * DK - 1);
+            const int tok = e / DK, i = e - tok * DK;
+            const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
+            rv[j] = ld(r, t * r_stride + c);
+            kv[j] = ld(k, t * k_stride + c);
+            wv[j] = w[t * f_stride + c];
+            uv[j] = u[t * f_stride + c];
+            av[j] = au[t * f_stride + c];
         }
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
@@ -284,28 +292,12 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
                 const int at = tok * ROWLEN + row_at(i);
                 hb.r[at] = rv[j];
                 hb.k[at] = kv[j];
-                hb.w[at] = expf(-decay_rate * sigmoid_f(wv[j]));
-                hb.au[at] = sigmoid_f(av[j]);                 // times the unit key below
+                hb.w[at] = wv[j];
+                hb.u[at] = uv[j];
+                hb.au[at] = av[j];
             }
         }
         stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
-        loaders_sync();
-        const int lane = lt & 31;
-        for (int tok = lt >> 5; tok < nt; tok += WORKERS / 32) {      // unit keys: a warp a token
-            float ss = 0.f;
-            for (int i = lane; i < DK; i += 32) {
-                const float x = hb.k[tok * ROWLEN + row_at(i)];
-                ss = fmaf(x, x, ss);
-            }
-            ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss + unit_eps);
-            for (int i = lane; i < DK; i += 32) {
-                const int at = tok * ROWLEN + row_at(i);
-                const float u = hb.k[at] * inv;
-                hb.u[at] = u;
-                hb.au[at] *= u;
-            }
-        }
     };
 
     const bool col_ok = !loader && c0 + col < dv;
@@ -326,15 +318,18 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
             const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
             float* op = out + ((size_t)t0 * H + h) * dv + c0 + col;
             if (nt == TC) {
-#pragma unroll 4
+                float part[TC];                              // the outputs' sums batched, as in the gated kernel
+#pragma unroll
+                for (int tok = 0; tok < TC; ++tok) part[tok] = delta_token(S, hb, tok, rg, col);
+#pragma unroll
                 for (int tok = 0; tok < TC; ++tok) {
-                    const float o = delta_token(S, hb, tok, rg, col);
+                    const float o = group_sum(part[tok]);
                     if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
                 }
             } else {
 #pragma unroll 1
                 for (int tok = 0; tok < nt; ++tok) {
-                    const float o = delta_token(S, hb, tok, rg, col);
+                    const float o = group_sum(delta_token(S, hb, tok, rg, col));
                     if (rg == 0 && col_ok) op[(size_t)tok * H * dv] = o;
                 }
             }
@@ -355,44 +350,38 @@ RI_API int ri_recurrent_key_dim() { return DK; }
 RI_API int ri_recurrent_state_rows() { return DKP; }
 
 RI_API int ri_gated_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
-                         const float* z, int z_stride, const void* z_bias, int act_dtype, int w_dtype,
-                         float q_scale, float inv_tau, float* out, float* state, const int* cu_q,
-                         const int* state_slots, int entries, int H, int dv, void* stream) {
+                         const float* alpha, int a_stride, int act_dtype, float q_scale, float* out, float* state,
+                         const int* cu_q, const int* state_slots, int entries, int H, int dv, void* stream) {
     if (entries <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((dv + COLS - 1) / COLS, H, entries);
     const size_t smem = 2 * (size_t)half_floats(3) * sizeof(float);
-#define RI_GS(TA, TW) do { static bool allowed = false; \
-    if (!allowed) { RI_CHECKED(allow_shared(gated_scan_kernel<TA, TW>, smem)); allowed = true; } \
-    RI_CHECKED(ri_launch(gated_scan_kernel<TA, TW>, grid, dim3(THREADS), smem, s, (const TA*)q, q_stride, \
-        (const TA*)k, k_stride, (const TA*)v, v_stride, z, z_stride, (const TW*)z_bias, q_scale, inv_tau, out, state, \
+#define RI_GS(TA) do { static bool allowed = false; \
+    if (!allowed) { RI_CHECKED(allow_shared(gated_scan_kernel<TA>, smem)); allowed = true; } \
+    RI_CHECKED(ri_launch(gated_scan_kernel<TA>, grid, dim3(THREADS), smem, s, (const TA*)q, q_stride, \
+        (const TA*)k, k_stride, (const TA*)v, v_stride, alpha, a_stride, q_scale, out, state, \
         cu_q, state_slots, H, dv)); } while (0)
-    if (act_dtype == RI_BF16 && w_dtype == RI_BF16) RI_GS(bf16, bf16);
-    else if (act_dtype == RI_BF16) RI_GS(bf16, float);
-    else if (w_dtype == RI_BF16) RI_GS(float, bf16);
-    else RI_GS(float, float);
+    if (act_dtype == RI_BF16) RI_GS(bf16);
+    else RI_GS(float);
 #undef RI_GS
     return ri_launch_status();
 }
 
 RI_API int ri_delta_scan(const void* r, int r_stride, const void* k, int k_stride, const void* v, int v_stride,
-                         const void* za, int za_stride, const void* za_bias, const float* zw, int zw_stride,
-                         const void* zw_bias, int act_dtype, int w_dtype, float decay_rate, float unit_eps,
+                         const float* w, const float* u, const float* au, int f_stride, int act_dtype,
                          float* out, float* state, const int* cu_q, const int* state_slots, int entries, int H,
                          int dv, void* stream) {
     if (entries <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((dv + COLS - 1) / COLS, H, entries);
     const size_t smem = 2 * (size_t)half_floats(5) * sizeof(float);
-#define RI_DS(TA, TW) do { static bool allowed = false; \
-    if (!allowed) { RI_CHECKED(allow_shared(delta_scan_kernel<TA, TW>, smem)); allowed = true; } \
-    RI_CHECKED(ri_launch(delta_scan_kernel<TA, TW>, grid, dim3(THREADS), smem, s, (const TA*)r, r_stride, \
-        (const TA*)k, k_stride, (const TA*)v, v_stride, (const TA*)za, za_stride, (const TW*)za_bias, zw, zw_stride, \
-        (const TW*)zw_bias, decay_rate, unit_eps, out, state, cu_q, state_slots, H, dv)); } while (0)
-    if (act_dtype == RI_BF16 && w_dtype == RI_BF16) RI_DS(bf16, bf16);
-    else if (act_dtype == RI_BF16) RI_DS(bf16, float);
-    else if (w_dtype == RI_BF16) RI_DS(float, bf16);
-    else RI_DS(float, float);
+#define RI_DS(TA) do { static bool allowed = false; \
+    if (!allowed) { RI_CHECKED(allow_shared(delta_scan_kernel<TA>, smem)); allowed = true; } \
+    RI_CHECKED(ri_launch(delta_scan_kernel<TA>, grid, dim3(THREADS), smem, s, (const TA*)r, r_stride, \
+        (const TA*)k, k_stride, (const TA*)v, v_stride, w, u, au, f_stride, out, state, cu_q, state_slots, H, dv)); \
+    } while (0)
+    if (act_dtype == RI_BF16) RI_DS(bf16);
+    else RI_DS(float);
 #undef RI_DS
     return ri_launch_status();
 }

@@ -207,6 +207,55 @@ __global__ void scaled_sum_kernel(const TA* __restrict__ a, const TA* __restrict
         out[i] = from_f32<TA>(sa * to_f32<TA>(a[i]) + sb * to_f32<TA>(b[i]));
 }
 
+// ------------------------------------------------ what the linear-attention recurrences are fed
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// z [T, n] fp32, in place: z <- sigmoid(z + bias)^(1/tau), formed as exp(log_sigmoid(.) / tau) so that a
+// decay close to one keeps its distance from one.
+template <typename TW>
+__global__ void gated_decay_kernel(float* __restrict__ z, const TW* __restrict__ bias, float inv_tau, long long total, int n) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const float x = z[i] + (bias ? to_f32<TW>(bias[i % n]) : 0.f);
+        z[i] = expf(log_sigmoid_f(x) * inv_tau);
+    }
+}
+
+// One warp per (token, head) of a delta-rule mixer: from the key k [dk], the logits of the removal rate
+// za [dk] and of the decay zw [dk] (fp32, in place) it makes
+//   zw <- exp(-decay_rate * sigmoid(zw + zw_bias)),  u = k / sqrt(|k|^2 + unit_eps),  au = sigmoid(za + za_bias) * u.
+template <typename TA, typename TW>
+__global__ void delta_prepare_kernel(const TA* __restrict__ k, int k_stride, const TA* __restrict__ za, int za_stride,
+                                     const TW* __restrict__ za_bias, float* __restrict__ zw, const TW* __restrict__ zw_bias,
+                                     float decay_rate, float unit_eps, float* __restrict__ u, float* __restrict__ au,
+                                     int tokens, int H, int dk) {
+    pdl_trigger();
+    pdl_wait();
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * warps + (threadIdx.x >> 5);
+    if (item >= (long long)tokens * H) return;
+    const int t = (int)(item / H), hh = (int)(item % H);
+    const TA* kp = k + (size_t)t * k_stride + (size_t)hh * dk;
+    const TA* ap = za + (size_t)t * za_stride + (size_t)hh * dk;
+    const size_t base = ((size_t)t * H + hh) * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+        const float x = to_f32<TA>(kp[i]);
+        ss = fmaf(x, x, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + unit_eps);
+    for (int i = lane; i < dk; i += 32) {
+        const int c = hh * dk + i;
+        const float unit = to_f32<TA>(kp[i]) * inv;
+        u[base + i] = unit;
+        au[base + i] = sigmoid_f(to_f32<TA>(ap[i]) + (za_bias ? to_f32<TW>(za_bias[c]) : 0.f)) * unit;
+        zw[base + i] = expf(-decay_rate * sigmoid_f(zw[base + i] + (zw_bias ? to_f32<TW>(zw_bias[c]) : 0.f)));
+    }
+}
+
 inline int ew_blocks(long long n) { return (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8); }
 }  // namespace
 
@@ -315,5 +364,34 @@ RI_API int ri_scaled_sum(const void* a, const void* b, float sa, float sb, void*
     else
         RI_CHECKED(ri_launch(scaled_sum_kernel<float>, dim3(ew_blocks(n)), dim3(256), 0, s, (const float*)a,
                              (const float*)b, sa, sb, (float*)out, n));
+    return ri_launch_status();
+}
+
+RI_API int ri_gated_decay(float* z, const void* bias, int w_dtype, float inv_tau, int tokens, int n, void* stream) {
+    const long long total = (long long)tokens * n;
+    if (total <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w_dtype == RI_BF16)
+        RI_CHECKED(ri_launch(gated_decay_kernel<bf16>, dim3(ew_blocks(total)), dim3(256), 0, s, z, (const bf16*)bias, inv_tau, total, n));
+    else
+        RI_CHECKED(ri_launch(gated_decay_kernel<float>, dim3(ew_blocks(total)), dim3(256), 0, s, z, (const float*)bias, inv_tau, total, n));
+    return ri_launch_status();
+}
+
+RI_API int ri_delta_prepare(const void* k, int k_stride, const void* za, int za_stride, const void* za_bias, float* zw,
+                            const void* zw_bias, int act_dtype, int w_dtype, float decay_rate, float unit_eps, float* u,
+                            float* au, int tokens, int H, int dk, void* stream) {
+    if (tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long items = (long long)tokens * H;
+    const int warps = 4;
+    const dim3 grid((unsigned)((items + warps - 1) / warps));
+#define RI_DP(TA, TW) RI_CHECKED(ri_launch(delta_prepare_kernel<TA, TW>, grid, dim3(32 * warps), 0, s, (const TA*)k, k_stride, \
+        (const TA*)za, za_stride, (const TW*)za_bias, zw, (const TW*)zw_bias, decay_rate, unit_eps, u, au, tokens, H, dk))
+    if (act_dtype == RI_BF16 && w_dtype == RI_BF16) RI_DP(bf16, bf16);
+    else if (act_dtype == RI_BF16) RI_DP(bf16, float);
+    else if (w_dtype == RI_BF16) RI_DP(float, bf16);
+    else RI_DP(float, float);
+#undef RI_DP
     return ri_launch_status();
 }

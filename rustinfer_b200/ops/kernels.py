@@ -592,19 +592,21 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
                state_slots: torch.Tensor, entries: int, num_heads: int, key_dim: int, value_dim: int) -> None:
     """Gated linear attention over every entry's tokens in order, from and into state[slot]:
     S = diag(sigmoid(z + z_bias)^(1/tau)) S + k v^T, out = S^T (q * q_scale).  q, k [T, H*dk], v [T, H*dv]
-    (column views allowed), z fp32 [T, H*dk]; state [slots, H, dv, recurrent_state_rows(dk)]."""
+    (column views allowed), z fp32 [T, H*dk]; state [slots, H, dv, recurrent_state_rows(dk)].  Two
+    launches: the decays of all tokens at once (z is overwritten with them), then the walk."""
     require_cuda(q, k, v, z, z_bias, out, state, cu_q, state_slots)
     T, H, dk, dv = q.shape[0], num_heads, key_dim, value_dim
     _scan_common(state, out, cu_q, state_slots, T, H, dk, dv, "gated_scan")
     _cols(q, T, H * dk, q.dtype, "gated_scan: q"); _cols(k, T, H * dk, q.dtype, "gated_scan: k")
     _cols(v, T, H * dv, q.dtype, "gated_scan: v"); _cols(z, T, H * dk, torch.float32, "gated_scan: z")
+    _contig(z, "z")
     if z_bias is not None and z_bias.numel() != H * dk:
         raise KernelError("gated_scan: z_bias has H*dk elements")
+    check(L.core().ri_gated_decay(_p(z), _p(z_bias), dtype_code(z_bias.dtype) if z_bias is not None else 0,
+                                  1.0 / float(tau), T, H * dk, stream_ptr()), "gated_decay")
     check(L.recurrent(dk).ri_gated_scan(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(z), z.stride(0),
-                                        _p(z_bias), dtype_code(q.dtype),
-                                        dtype_code(z_bias.dtype) if z_bias is not None else 0, float(q_scale),
-                                        1.0 / float(tau), _p(out), _p(state), _p(cu_q), _p(state_slots), int(entries),
-                                        H, dv, stream_ptr()), "gated_scan")
+                                        dtype_code(q.dtype), float(q_scale), _p(out), _p(state), _p(cu_q),
+                                        _p(state_slots), int(entries), H, dv, stream_ptr()), "gated_scan")
 
 
 def delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, za: torch.Tensor, za_bias: Optional[torch.Tensor],
@@ -613,22 +615,27 @@ def delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, za: torch.Tens
                num_heads: int, key_dim: int, value_dim: int) -> None:
     """Delta rule with a decay, over every entry's tokens in order, from and into state[slot]:
     S = diag(w) S - (a * u)(u^T S) + k v^T, out = S^T r, with u = k / sqrt(|k|^2 + unit_eps),
-    w = exp(-decay_rate * sigmoid(zw + zw_bias)), a = sigmoid(za + za_bias).  zw is fp32."""
+    w = exp(-decay_rate * sigmoid(zw + zw_bias)), a = sigmoid(za + za_bias).  zw is fp32 and is
+    overwritten with the decays.  Two launches: w, u and a * u of all tokens at once, then the walk."""
     require_cuda(r, k, v, za, za_bias, zw, zw_bias, out, state, cu_q, state_slots)
     T, H, dk, dv = r.shape[0], num_heads, key_dim, value_dim
     _scan_common(state, out, cu_q, state_slots, T, H, dk, dv, "delta_scan")
     for t, n, what in ((r, H * dk, "r"), (k, H * dk, "k"), (v, H * dv, "v"), (za, H * dk, "za")):
         _cols(t, T, n, r.dtype, "delta_scan: " + what)
     _cols(zw, T, H * dk, torch.float32, "delta_scan: zw")
+    _contig(zw, "zw")
     biases = [b for b in (za_bias, zw_bias) if b is not None]
     for b in biases:
         if b.numel() != H * dk or b.dtype != biases[0].dtype:
             raise KernelError("delta_scan: biases have H*dk elements and one dtype")
-    check(L.recurrent(dk).ri_delta_scan(_p(r), r.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(za), za.stride(0),
-                                        _p(za_bias), _p(zw), zw.stride(0), _p(zw_bias), dtype_code(r.dtype),
-                                        dtype_code(biases[0].dtype) if biases else 0, float(decay_rate),
-                                        float(unit_eps), _p(out), _p(state), _p(cu_q), _p(state_slots), int(entries),
-                                        H, dv, stream_ptr()), "delta_scan")
+    unit = torch.empty((2, T, H * dk), dtype=torch.float32, device=r.device)      # u, a * u
+    check(L.core().ri_delta_prepare(_p(k), k.stride(0), _p(za), za.stride(0), _p(za_bias), _p(zw), _p(zw_bias),
+                                    dtype_code(r.dtype), dtype_code(biases[0].dtype) if biases else 0,
+                                    float(decay_rate), float(unit_eps), _p(unit[0]), _p(unit[1]), T, H, dk,
+                                    stream_ptr()), "delta_prepare")
+    check(L.recurrent(dk).ri_delta_scan(_p(r), r.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(zw), _p(unit[0]),
+                                        _p(unit[1]), H * dk, dtype_code(r.dtype), _p(out), _p(state), _p(cu_q),
+                                        _p(state_slots), int(entries), H, dv, stream_ptr()), "delta_scan")
 
 
 def _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim):
