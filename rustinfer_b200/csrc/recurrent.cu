@@ -56,6 +56,17 @@ __device__ __forceinline__ float group_sum(float v) {
 template <typename T>
 __device__ __forceinline__ float ld(const T* p, size_t i) { return to_f32<T>(p[i]); }
 
+// four consecutive elements from an address that is a multiple of four elements
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float4 scaled(float4 v, float s) { return make_float4(v.x * s, v.y * s, v.z * s, v.w * s); }
+constexpr int PER4 = (TC * DK / 4 + WORKERS - 1) / WORKERS;   // groups of four elements a loading thread stages per round
+
 __device__ __forceinline__ void load_state(float (&S)[NR], const float* sp, bool ok) {
 #pragma unroll
     for (int m = 0; m < NR / 4; ++m) {
@@ -115,7 +126,7 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
                   const TA* __restrict__ v, int v_stride, const float* __restrict__ alpha, int a_stride,
                   float q_scale, float* __restrict__ out,
                   float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
-                  int H, int dv) {
+                  int H, int dv, int vec) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
@@ -135,6 +146,31 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
     auto stage = [&](int round) {
         const GatedHalf hb(smem + (round & 1) * HALF);
         const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+        if (vec) {                                           // four elements a load, four a store
+            float4 qv[PER4], kv[PER4], av[PER4];
+#pragma unroll
+            for (int j = 0; j < PER4; ++j) {
+                const int e = min(lt + j * WORKERS, nt * (DK / 4) - 1);
+                const int tok = e / (DK / 4), i = (e - tok * (DK / 4)) * 4;
+                const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
+                qv[j] = ld4(q + t * q_stride + c);
+                kv[j] = ld4(k + t * k_stride + c);
+                av[j] = ld4(alpha + t * a_stride + c);
+            }
+#pragma unroll
+            for (int j = 0; j < PER4; ++j) {
+                const int e = lt + j * WORKERS;
+                if (e < nt * (DK / 4)) {
+                    const int tok = e / (DK / 4), i = (e - tok * (DK / 4)) * 4;
+                    const int at = tok * ROWLEN + row_at(i);
+                    *reinterpret_cast<float4*>(hb.q + at) = scaled(qv[j], q_scale);
+                    *reinterpret_cast<float4*>(hb.k + at) = kv[j];
+                    *reinterpret_cast<float4*>(hb.a + at) = av[j];
+                }
+            }
+            stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
+            return;
+        }
         // every load of the round is issued before the first is used: addresses past the round's
         // end are clamped to its last element (read again, stored nowhere) so that no load is conditional
         float qv[PER], kv[PER], av[PER];
@@ -252,7 +288,7 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
                   const TA* __restrict__ v, int v_stride, const float* __restrict__ w, const float* __restrict__ u,
                   const float* __restrict__ au, int f_stride, float* __restrict__ out,
                   float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
-                  int H, int dv) {
+                  int H, int dv, int vec) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
@@ -272,6 +308,35 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
     auto stage = [&](int round) {
         const DeltaHalf hb(smem + (round & 1) * HALF);
         const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+        if (vec) {
+            float4 rv[PER4], kv[PER4], wv[PER4], uv[PER4], av[PER4];
+#pragma unroll
+            for (int j = 0; j < PER4; ++j) {
+                const int e = min(lt + j * WORKERS, nt * (DK / 4) - 1);
+                const int tok = e / (DK / 4), i = (e - tok * (DK / 4)) * 4;
+                const size_t t = (size_t)(t0 + tok), c = (size_t)h * DK + i;
+                rv[j] = ld4(r + t * r_stride + c);
+                kv[j] = ld4(k + t * k_stride + c);
+                wv[j] = ld4(w + t * f_stride + c);
+                uv[j] = ld4(u + t * f_stride + c);
+                av[j] = ld4(au + t * f_stride + c);
+            }
+#pragma unroll
+            for (int j = 0; j < PER4; ++j) {
+                const int e = lt + j * WORKERS;
+                if (e < nt * (DK / 4)) {
+                    const int tok = e / (DK / 4), i = (e - tok * (DK / 4)) * 4;
+                    const int at = tok * ROWLEN + row_at(i);
+                    *reinterpret_cast<float4*>(hb.r + at) = rv[j];
+                    *reinterpret_cast<float4*>(hb.k + at) = kv[j];
+                    *reinterpret_cast<float4*>(hb.w + at) = wv[j];
+                    *reinterpret_cast<float4*>(hb.u + at) = uv[j];
+                    *reinterpret_cast<float4*>(hb.au + at) = av[j];
+                }
+            }
+            stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
+            return;
+        }
         float rv[PER], kv[PER], wv[PER], uv[PER], av[PER];      // loads unconditional, as in the gated kernel
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
@@ -339,6 +404,112 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
     if (col_ok) store_state(S, sp);
 }
 
+// ------------------------------------------------------------- entries of a single token
+// A step in which every entry brings one token (decoding): no rounds and no staging.  A CTA of
+// WORKERS threads owns COLS value channels of one head of one entry; a lane reads its rows of the
+// token's vectors straight from global memory, in the same order and with the same arithmetic as
+// the walk above, so a token's bits do not depend on which kernel took it.
+template <typename TA>
+__device__ __forceinline__ void rows_of(float (&x)[NR], const TA* p, int rg, float scale) {
+#pragma unroll
+    for (int n = 0; n < NR; ++n) {
+        const int i = rg * NR + n;
+        x[n] = i < DK ? to_f32<TA>(p[i]) * scale : 0.f;
+    }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(WORKERS)
+gated_step_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__ k, int k_stride,
+                  const TA* __restrict__ v, int v_stride, const float* __restrict__ alpha, int a_stride,
+                  float q_scale, float* __restrict__ out, float* __restrict__ state,
+                  const int* __restrict__ cu_q, const int* __restrict__ state_slots, int H, int dv) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
+    const int col = threadIdx.x / R, rg = threadIdx.x % R;
+    const int t = cu_q[b];
+    if (cu_q[b + 1] - t != 1) return;                        // the host sends only steps of single tokens here
+    const bool col_ok = c0 + col < dv;
+    float* sp = state + ((((size_t)state_slots[b] * H + h) * dv + c0 + col) * DKP + rg * NR);
+    float S[NR], a[NR], kk[NR], qq[NR];
+    load_state(S, sp, col_ok);
+    rows_of(a, alpha + (size_t)t * a_stride + (size_t)h * DK, rg, 1.f);
+    rows_of(kk, k + (size_t)t * k_stride + (size_t)h * DK, rg, 1.f);
+    rows_of(qq, q + (size_t)t * q_stride + (size_t)h * DK, rg, q_scale);
+    const float vj = col_ok ? to_f32<TA>(v[(size_t)t * v_stride + (size_t)h * dv + c0 + col]) : 0.f;
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m) {
+        S[4 * m + 0] = fmaf(a[4 * m + 0], S[4 * m + 0], kk[4 * m + 0] * vj);
+        S[4 * m + 1] = fmaf(a[4 * m + 1], S[4 * m + 1], kk[4 * m + 1] * vj);
+        S[4 * m + 2] = fmaf(a[4 * m + 2], S[4 * m + 2], kk[4 * m + 2] * vj);
+        S[4 * m + 3] = fmaf(a[4 * m + 3], S[4 * m + 3], kk[4 * m + 3] * vj);
+        o0 = fmaf(S[4 * m + 0], qq[4 * m + 0], o0);
+        o1 = fmaf(S[4 * m + 1], qq[4 * m + 1], o1);
+        o0 = fmaf(S[4 * m + 2], qq[4 * m + 2], o0);
+        o1 = fmaf(S[4 * m + 3], qq[4 * m + 3], o1);
+    }
+    const float o = group_sum(o0 + o1);
+    if (col_ok) {
+        if (rg == 0) out[((size_t)t * H + h) * dv + c0 + col] = o;
+        store_state(S, sp);
+    }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(WORKERS)
+delta_step_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__ k, int k_stride,
+                  const TA* __restrict__ v, int v_stride, const float* __restrict__ w, const float* __restrict__ u,
+                  const float* __restrict__ au, int f_stride, float* __restrict__ out, float* __restrict__ state,
+                  const int* __restrict__ cu_q, const int* __restrict__ state_slots, int H, int dv) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * COLS;
+    const int col = threadIdx.x / R, rg = threadIdx.x % R;
+    const int t = cu_q[b];
+    if (cu_q[b + 1] - t != 1) return;
+    const bool col_ok = c0 + col < dv;
+    float* sp = state + ((((size_t)state_slots[b] * H + h) * dv + c0 + col) * DKP + rg * NR);
+    float S[NR], x[NR];
+    load_state(S, sp, col_ok);
+    const size_t f = (size_t)t * f_stride + (size_t)h * DK;
+    rows_of(x, u + f, rg, 1.f);
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m) {
+        d0 = fmaf(x[4 * m + 0], S[4 * m + 0], d0);
+        d1 = fmaf(x[4 * m + 1], S[4 * m + 1], d1);
+        d0 = fmaf(x[4 * m + 2], S[4 * m + 2], d0);
+        d1 = fmaf(x[4 * m + 3], S[4 * m + 3], d1);
+    }
+    const float dot = group_sum(d0 + d1);
+    float ww[NR], aa[NR], kk[NR];
+    rows_of(ww, w + f, rg, 1.f);
+    rows_of(aa, au + f, rg, 1.f);
+    rows_of(kk, k + (size_t)t * k_stride + (size_t)h * DK, rg, 1.f);
+    rows_of(x, r + (size_t)t * r_stride + (size_t)h * DK, rg, 1.f);
+    const float vj = col_ok ? to_f32<TA>(v[(size_t)t * v_stride + (size_t)h * dv + c0 + col]) : 0.f;
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < NR / 4; ++m) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            S[4 * m + e] = fmaf(ww[4 * m + e], S[4 * m + e], fmaf(-aa[4 * m + e], dot, kk[4 * m + e] * vj));
+        o0 = fmaf(S[4 * m + 0], x[4 * m + 0], o0);
+        o1 = fmaf(S[4 * m + 1], x[4 * m + 1], o1);
+        o0 = fmaf(S[4 * m + 2], x[4 * m + 2], o0);
+        o1 = fmaf(S[4 * m + 3], x[4 * m + 3], o1);
+    }
+    const float o = group_sum(o0 + o1);
+    if (col_ok) {
+        if (rg == 0) out[((size_t)t * H + h) * dv + c0 + col] = o;
+        store_state(S, sp);
+    }
+}
+
+inline bool aligned4(const void* p, int esize) { return (reinterpret_cast<uintptr_t>(p) % (4 * (size_t)esize)) == 0; }
+
 template <typename Kernel>
 int allow_shared(Kernel kernel, size_t bytes) {
     if (bytes <= 48 * 1024) return 0;
@@ -349,18 +520,29 @@ int allow_shared(Kernel kernel, size_t bytes) {
 RI_API int ri_recurrent_key_dim() { return DK; }
 RI_API int ri_recurrent_state_rows() { return DKP; }
 
+// `single` != 0: every entry brings exactly one token (the kernel without staging takes the step)
 RI_API int ri_gated_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
                          const float* alpha, int a_stride, int act_dtype, float q_scale, float* out, float* state,
-                         const int* cu_q, const int* state_slots, int entries, int H, int dv, void* stream) {
+                         const int* cu_q, const int* state_slots, int entries, int H, int dv, int single,
+                         void* stream) {
     if (entries <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((dv + COLS - 1) / COLS, H, entries);
     const size_t smem = 2 * (size_t)half_floats(3) * sizeof(float);
-#define RI_GS(TA) do { static bool allowed = false; \
+    const int esize = act_dtype == RI_BF16 ? 2 : 4;
+    const int vec = DK % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && a_stride % 4 == 0 &&
+                    aligned4(q, esize) && aligned4(k, esize) && aligned4(alpha, 4);
+#define RI_GS(TA) do { \
+    if (single) { \
+        RI_CHECKED(ri_launch(gated_step_kernel<TA>, grid, dim3(WORKERS), 0, s, (const TA*)q, q_stride, (const TA*)k, \
+            k_stride, (const TA*)v, v_stride, alpha, a_stride, q_scale, out, state, cu_q, state_slots, H, dv)); \
+        break; \
+    } \
+    static bool allowed = false; \
     if (!allowed) { RI_CHECKED(allow_shared(gated_scan_kernel<TA>, smem)); allowed = true; } \
     RI_CHECKED(ri_launch(gated_scan_kernel<TA>, grid, dim3(THREADS), smem, s, (const TA*)q, q_stride, \
         (const TA*)k, k_stride, (const TA*)v, v_stride, alpha, a_stride, q_scale, out, state, \
-        cu_q, state_slots, H, dv)); } while (0)
+        cu_q, state_slots, H, dv, vec)); } while (0)
     if (act_dtype == RI_BF16) RI_GS(bf16);
     else RI_GS(float);
 #undef RI_GS
@@ -370,15 +552,24 @@ RI_API int ri_gated_scan(const void* q, int q_stride, const void* k, int k_strid
 RI_API int ri_delta_scan(const void* r, int r_stride, const void* k, int k_stride, const void* v, int v_stride,
                          const float* w, const float* u, const float* au, int f_stride, int act_dtype,
                          float* out, float* state, const int* cu_q, const int* state_slots, int entries, int H,
-                         int dv, void* stream) {
+                         int dv, int single, void* stream) {
     if (entries <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((dv + COLS - 1) / COLS, H, entries);
     const size_t smem = 2 * (size_t)half_floats(5) * sizeof(float);
-#define RI_DS(TA) do { static bool allowed = false; \
+    const int esize = act_dtype == RI_BF16 ? 2 : 4;
+    const int vec = DK % 4 == 0 && r_stride % 4 == 0 && k_stride % 4 == 0 && f_stride % 4 == 0 &&
+                    aligned4(r, esize) && aligned4(k, esize) && aligned4(w, 4) && aligned4(u, 4) && aligned4(au, 4);
+#define RI_DS(TA) do { \
+    if (single) { \
+        RI_CHECKED(ri_launch(delta_step_kernel<TA>, grid, dim3(WORKERS), 0, s, (const TA*)r, r_stride, (const TA*)k, \
+            k_stride, (const TA*)v, v_stride, w, u, au, f_stride, out, state, cu_q, state_slots, H, dv)); \
+        break; \
+    } \
+    static bool allowed = false; \
     if (!allowed) { RI_CHECKED(allow_shared(delta_scan_kernel<TA>, smem)); allowed = true; } \
     RI_CHECKED(ri_launch(delta_scan_kernel<TA>, grid, dim3(THREADS), smem, s, (const TA*)r, r_stride, \
-        (const TA*)k, k_stride, (const TA*)v, v_stride, w, u, au, f_stride, out, state, cu_q, state_slots, H, dv)); \
+        (const TA*)k, k_stride, (const TA*)v, v_stride, w, u, au, f_stride, out, state, cu_q, state_slots, H, dv, vec)); \
     } while (0)
     if (act_dtype == RI_BF16) RI_DS(bf16);
     else RI_DS(float);

@@ -593,7 +593,8 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
     """Gated linear attention over every entry's tokens in order, from and into state[slot]:
     S = diag(sigmoid(z + z_bias)^(1/tau)) S + k v^T, out = S^T (q * q_scale).  q, k [T, H*dk], v [T, H*dv]
     (column views allowed), z fp32 [T, H*dk]; state [slots, H, dv, recurrent_state_rows(dk)].  Two
-    launches: the decays of all tokens at once (z is overwritten with them), then the walk."""
+    launches: the decays of all tokens at once (z is overwritten with them), then the walk (a step in
+    which every entry brings one token, T == entries, goes to the kernel without staging)."""
     require_cuda(q, k, v, z, z_bias, out, state, cu_q, state_slots)
     T, H, dk, dv = q.shape[0], num_heads, key_dim, value_dim
     _scan_common(state, out, cu_q, state_slots, T, H, dk, dv, "gated_scan")
@@ -606,7 +607,8 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
                                   1.0 / float(tau), T, H * dk, stream_ptr()), "gated_decay")
     check(L.recurrent(dk).ri_gated_scan(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(z), z.stride(0),
                                         dtype_code(q.dtype), float(q_scale), _p(out), _p(state), _p(cu_q),
-                                        _p(state_slots), int(entries), H, dv, stream_ptr()), "gated_scan")
+                                        _p(state_slots), int(entries), H, dv, 1 if T == int(entries) else 0,
+                                        stream_ptr()), "gated_scan")
 
 
 def delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, za: torch.Tensor, za_bias: Optional[torch.Tensor],
@@ -635,7 +637,8 @@ def delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, za: torch.Tens
                                     stream_ptr()), "delta_prepare")
     check(L.recurrent(dk).ri_delta_scan(_p(r), r.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(zw), _p(unit[0]),
                                         _p(unit[1]), H * dk, dtype_code(r.dtype), _p(out), _p(state), _p(cu_q),
-                                        _p(state_slots), int(entries), H, dv, stream_ptr()), "delta_scan")
+                                        _p(state_slots), int(entries), H, dv, 1 if T == int(entries) else 0,
+                                        stream_ptr()), "delta_scan")
 
 
 def _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim):

@@ -45,8 +45,8 @@ _SIGNATURES = {
     "ri_gated_head_norm": [_P, _P, _I, _P, _I, _I, _I, _F, _P, _I, _I, _I, _I, _P],
     "ri_activation": [_P, _P, _I, _L, _I, _P],
     "ri_scaled_sum": [_P, _P, _F, _F, _P, _I, _L, _P],
-    "ri_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _I, _I, _P],
-    "ri_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "ri_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "ri_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ri_gated_decay": [_P, _P, _I, _F, _I, _I, _P],
     "ri_delta_prepare": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _F, _F, _P, _P, _I, _I, _I, _P],
 }
