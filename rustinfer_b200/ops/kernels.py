@@ -559,9 +559,9 @@ _rows_checked = set()
 
 def recurrent_state_rows(key_dim: int) -> int:
     """Rows a stored column of the recurrences' state has: the key size rounded up so that each of the
-    lanes that share a column (4 up to a key size of 64, 8 above) holds a multiple of 4 rows.  The
-    state of one request and head is [value_dim, rows] fp32; rows beyond key_dim stay zero."""
-    lanes = 4 if key_dim <= 64 else 8
+    lanes that share a column (4, 8, 16 or 32: as few as leave a lane at most 4 rows) holds a multiple
+    of 4 rows.  The state of one request and head is [value_dim, rows] fp32; rows beyond key_dim stay zero."""
+    lanes = 4 if key_dim <= 16 else 8 if key_dim <= 32 else 16 if key_dim <= 64 else 32
     per_lane = -(-(-(-key_dim // lanes)) // 4) * 4
     return lanes * per_lane
 
