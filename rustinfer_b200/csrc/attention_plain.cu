@@ -93,25 +93,21 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     const size_t k_base = (size_t)g * page_size * HD;
     for (int kb = (lo_tile / KC) * KC; kb <= p_last; kb += KC) {
         __syncthreads();                                 // previous chunk's Vs/Ps reads are done
-        for (int e = tid; e < KC * HD; e += THREADS) {
-            const int kk = e / HD, d = e - kk * HD;
+        // a warp a key: the page is looked up once per key and the lanes read along the head
+        for (int kk = tid >> 5; kk < KC; kk += THREADS / 32) {
             const int key = kb + kk;
-            float kval = 0.f;
-            if (key >= lo_tile && key <= p_last) {
-                const int page = bt[key / page_size], off = key % page_size;
-                kval = to_f32<T>(cache[(size_t)page * page_elems + k_base + (size_t)off * HD + d]);
+            const bool seen = key >= lo_tile && key <= p_last;
+            const T* kp = cache;
+            const T* vp = cache;
+            if (seen) {
+                const int blk = key / page_size;
+                const size_t page = (size_t)bt[blk] * page_elems;
+                const int off = key - blk * page_size;
+                kp = cache + page + k_base + (size_t)off * HD;
+                vp = cache + page + v_base + (size_t)off * VD;
             }
-            Ks[kk * KS + d] = kval;
-        }
-        for (int e = tid; e < KC * VD; e += THREADS) {
-            const int kk = e / VD, d = e - kk * VD;
-            const int key = kb + kk;
-            float vval = 0.f;
-            if (key >= lo_tile && key <= p_last) {
-                const int page = bt[key / page_size], off = key % page_size;
-                vval = to_f32<T>(cache[(size_t)page * page_elems + v_base + (size_t)off * VD + d]);
-            }
-            Vs[kk * VD + d] = vval;
+            for (int d = tid & 31; d < HD; d += 32) Ks[kk * KS + d] = seen ? to_f32<T>(kp[d]) : 0.f;
+            for (int d = tid & 31; d < VD; d += 32) Vs[kk * VD + d] = seen ? to_f32<T>(vp[d]) : 0.f;
         }
         __syncthreads();
 
