@@ -167,6 +167,140 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     }
 }
 
+// ------------------------------------------------------------------ entries of a single token
+// One CTA per (kv head, entry that brings one token): the G query heads of the kv head share every
+// key and value it reads.  Keys are taken in chunks of SK with a running maximum and sum per head
+// (fp32 throughout): a thread a key for the scores (q in shared memory, a key element serves all G
+// heads), a warp a head for the chunk's maximum and weights, a warp a key and a lane a value channel
+// for the weighted sum, the warps' parts added at the end.  Same mask as above: keys lo .. p with
+// lo the later of the window's and the block's start.
+constexpr int SK = 512;                        // keys per chunk
+constexpr int SG = 16;                         // most query heads a kv head
+constexpr int SV = (VD + 31) / 32;             // value channels a lane
+constexpr size_t SINGLE_SMEM_FLOATS = (size_t)SG * HD + (size_t)SG * SK + 3 * SG + (size_t)(THREADS / 32) * SG * VD;
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                        const T* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
+                        const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                        const int* __restrict__ entry_list, int Hq, int Hkv, int page_size, float scale,
+                        int window, int block) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float smem[];
+    const int G = Hq / Hkv;
+    float* qs = smem;                                    // [G][HD]
+    float* sc = qs + SG * HD;                            // [G][SK]
+    float* mrun = sc + SG * SK;                          // [G] running maximum
+    float* lrun = mrun + SG;                             // [G] running sum
+    float* arun = lrun + SG;                             // [G] what the chunk rescales the old sums by
+    float* red = arun + SG;                              // [warps][G][VD]
+    const int kvh = blockIdx.x;
+    const int b = entry_list[blockIdx.y];
+    if (b < 0) return;
+    const int t = cu_q[b];
+    if (cu_q[b + 1] - t != 1) return;
+    const int p = kv_len[b] - 1;
+    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    if (block > 0) lo = max(lo, (p / block) * block);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int WARPS = THREADS / 32;
+    for (int e = tid; e < G * HD; e += THREADS)
+        qs[e] = to_f32<T>(q[(size_t)t * q_stride + (size_t)kvh * G * HD + e]);
+    if (tid < G) { mrun[tid] = -INFINITY; lrun[tid] = 0.f; }
+    float acc[SG][SV];
+#pragma unroll
+    for (int g = 0; g < SG; ++g)
+#pragma unroll
+        for (int i = 0; i < SV; ++i) acc[g][i] = 0.f;
+    const int* bt = block_table + (size_t)b * table_stride;
+    const size_t page_elems = (size_t)Hkv * page_size * (HD + VD);
+    const size_t v_base = (size_t)Hkv * page_size * HD + (size_t)kvh * page_size * VD;
+    const size_t k_base = (size_t)kvh * page_size * HD;
+    __syncthreads();
+    for (int k0 = lo; k0 <= p; k0 += SK) {
+        const int n = min(SK, p - k0 + 1);
+        // scores of the chunk: a thread a key
+        for (int kk = tid; kk < n; kk += THREADS) {
+            const int key = k0 + kk, blk = key / page_size;
+            const T* kp = cache + (size_t)bt[blk] * page_elems + k_base + (size_t)(key - blk * page_size) * HD;
+            float s[SG];
+#pragma unroll
+            for (int g = 0; g < SG; ++g) s[g] = 0.f;
+            for (int d = 0; d < HD; ++d) {
+                const float kd = to_f32<T>(kp[d]);
+#pragma unroll
+                for (int g = 0; g < SG; ++g)
+                    if (g < G) s[g] = fmaf(qs[g * HD + d], kd, s[g]);
+            }
+#pragma unroll
+            for (int g = 0; g < SG; ++g)
+                if (g < G) sc[g * SK + kk] = s[g] * scale;
+        }
+        __syncthreads();
+        // the chunk's maximum, the weights and their sum: a warp a head
+        for (int g = warp; g < G; g += WARPS) {
+            float mx = -INFINITY;
+            for (int kk = lane; kk < n; kk += 32) mx = fmaxf(mx, sc[g * SK + kk]);
+            mx = warp_max(mx);
+            const float m_old = mrun[g], m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+            for (int kk = lane; kk < n; kk += 32) {
+                const float w = expf(sc[g * SK + kk] - m_new);
+                sc[g * SK + kk] = w;
+                sum += w;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                const float a = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                arun[g] = a;
+                lrun[g] = lrun[g] * a + sum;
+                mrun[g] = m_new;
+            }
+        }
+        __syncthreads();
+        // weighted sum of the values: a warp a key, a lane a value channel
+#pragma unroll
+        for (int g = 0; g < SG; ++g)
+            if (g < G) {
+                const float a = arun[g];
+#pragma unroll
+                for (int i = 0; i < SV; ++i) acc[g][i] *= a;
+            }
+        for (int kk = warp; kk < n; kk += WARPS) {
+            const int key = k0 + kk, blk = key / page_size;
+            const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD;
+            float v[SV];
+#pragma unroll
+            for (int i = 0; i < SV; ++i) v[i] = lane + 32 * i < VD ? to_f32<T>(vp[lane + 32 * i]) : 0.f;
+#pragma unroll
+            for (int g = 0; g < SG; ++g)
+                if (g < G) {
+                    const float w = sc[g * SK + kk];
+#pragma unroll
+                    for (int i = 0; i < SV; ++i) acc[g][i] = fmaf(w, v[i], acc[g][i]);
+                }
+        }
+        __syncthreads();                                 // sc and arun are free for the next chunk
+    }
+#pragma unroll
+    for (int g = 0; g < SG; ++g)
+        if (g < G) {
+#pragma unroll
+            for (int i = 0; i < SV; ++i)
+                if (lane + 32 * i < VD) red[((size_t)warp * SG + g) * VD + lane + 32 * i] = acc[g][i];
+        }
+    __syncthreads();
+    for (int e = tid; e < G * VD; e += THREADS) {
+        const int g = e / VD, d = e - g * VD;
+        float total = 0.f;
+        for (int w = 0; w < WARPS; ++w) total += red[((size_t)w * SG + g) * VD + d];
+        const float l = lrun[g];
+        out[(size_t)t * out_stride + (size_t)(kvh * G + g) * VD + d] = from_f32<T>(l > 0.f ? total / l : 0.f);
+    }
+}
+
 template <typename T>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* cache,
            const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
@@ -209,6 +343,38 @@ RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_st
                             kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, s);
     return launch<float>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
                          kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, s);
+}
+
+// Entries that bring a single token (entry_list[i], -1: skip): keys and values of a kv head are read once
+// for its query heads.  Returns cudaErrorNotSupported for more than 16 query heads a kv head or values
+// wider than 128 (the caller then uses the tiled kernel above, which takes everything).
+RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_stride, const void* cache, int dtype,
+                               const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
+                               const int* entry_list, int n_entries, int Hq, int Hkv, int page_size, float scale,
+                               int window, int block, void* stream) {
+    if (n_entries <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
+    if (Hq / Hkv > SG || SV > 4) return (int)cudaErrorNotSupported;
+    const size_t smem = SINGLE_SMEM_FLOATS * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(Hkv, n_entries);
+#define RI_SINGLE(T) do { static bool configured = false; \
+    if (!configured) { \
+        cudaError_t e = cudaFuncSetAttribute(attention_single_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e; \
+        configured = true; } \
+    RI_CHECKED(ri_launch(attention_single_kernel<T>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (T*)out, \
+        out_stride, (const T*)cache, block_table, table_stride, cu_q, kv_len, entry_list, Hq, Hkv, page_size, scale, \
+        window, block)); } while (0)
+    if (dtype == RI_BF16) RI_SINGLE(bf16);
+    else RI_SINGLE(float);
+#undef RI_SINGLE
+    return ri_launch_status();
+}
+
+RI_API int ri_attention_single_supports(int Hq, int Hkv) {
+    return Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= SG && SV <= 4 &&
+           SINGLE_SMEM_FLOATS * sizeof(float) <= 200 * 1024;
 }
 
 RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }

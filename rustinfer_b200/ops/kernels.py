@@ -419,6 +419,34 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
           "attention_plain")
 
 
+def attention_single_supports(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: Optional[int] = None) -> bool:
+    """Whether the single-token attention kernel takes this geometry (up to 16 query heads a kv head,
+    values up to 128 wide)."""
+    return bool(L.attention_plain(head_dim, value_dim or head_dim).ri_attention_single_supports(num_heads, num_kv_heads))
+
+
+def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                     cu_q: torch.Tensor, kv_len: torch.Tensor, entry_list: torch.Tensor, num_heads: int,
+                     num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+                     block: Optional[int] = None, value_dim: Optional[int] = None) -> None:
+    """Attention of the entries that bring one token (`entry_list`, int32; -1 skips): fp32 arithmetic, a kv
+    head's keys and values read once for all its query heads.  Arguments as `attention_plain`."""
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list)
+    for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"), (entry_list, "entry_list")):
+        _i32(t, n)
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != cache.dtype or out.dtype != cache.dtype:
+        raise KernelError("attention: q, out and cache share a dtype; q and out have unit column stride")
+    _contig(cache, "cache")
+    vd = value_dim or head_dim
+    page_size = paged_cache_page_size(cache, num_kv_heads, head_dim, vd)
+    lib = L.attention_plain(head_dim, vd)
+    check(lib.ri_attention_single(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), dtype_code(cache.dtype),
+                                  _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list),
+                                  entry_list.numel(), num_heads, num_kv_heads, page_size, float(scale),
+                                  int(window) if window else 0, int(block) if block else 0, stream_ptr()),
+          "attention_single")
+
+
 def paged_cache_page_size(cache: torch.Tensor, num_kv_heads: int, head_dim: int, value_dim: int) -> int:
     """Tokens a page of `cache` holds: [pages, 2, Hkv, page, hd] when keys and values have one size,
     [pages, Hkv * page * (hd + vd)] (a page's keys, then its values) when they differ."""

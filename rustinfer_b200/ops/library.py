@@ -39,6 +39,8 @@ _SIGNATURES = {
     "ri_decode_chain": [_P, _I, _P, _I, _P, _P, _I, _P],
     "ri_decode_chain_fits": [_P, _I, _I, _I],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "ri_attention_single": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "ri_attention_single_supports": [_I, _I],
     "ri_embed_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "ri_sandwich_norm": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _F, _P],
     "ri_head_norm_scatter": [_P, _I, _I, _P, _P, _I, _I, _F, _P, _P, _I, _I, _I, _I, _I, _I, _P],

@@ -121,15 +121,18 @@ class GQAAttention(Mixer):
         else:
             self._single = None
             self._tiles = token_tiles(16, skip_single_token=False)
-        # a mixer with the further options in bfloat16, keys and values of one size the tensor-core
-        # kernel is built for: prompt portions run there with fp32 softmax weights (three bf16 pieces
-        # each), single tokens stay on the fp32-arithmetic kernel
-        self.precise_mma = (self.general and ctx.dtype == torch.bfloat16 and self.vd == self.hd
-                            and self.hd % 16 == 0 and 16 <= self.hd <= L.MMA_MAX_HEAD_DIM
-                            and os.environ.get("RUSTINFER_B200_BLOCK_ATTENTION", "mma") != "plain")
-        if self.precise_mma:
+        # a mixer with the further options in bfloat16: entries of one token go to the kernel that reads a kv
+        # head's keys once for all its query heads; prompt portions run on the tensor-core kernel with fp32
+        # softmax weights (three bf16 pieces each) where keys and values have one size it is built for, else
+        # on the fp32-arithmetic kernel.  The 32-bit engine keeps the one kernel whose sums do not depend on the cut.
+        fast = (self.general and ctx.dtype == torch.bfloat16
+                and os.environ.get("RUSTINFER_B200_BLOCK_ATTENTION", "fast") != "plain")
+        self.precise_mma = (fast and self.vd == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= L.MMA_MAX_HEAD_DIM)
+        self.fast_single = fast and K.attention_single_supports(self.Hq, self.Hkv, self.hd, self.vd)
+        if self.precise_mma or self.fast_single:
             self._single = single_token_entries()
-            self._tiles = token_tiles(K.mma_tokens_per_tile(self.Hq, self.Hkv), skip_single_token=True)
+            rows = K.mma_tokens_per_tile(self.Hq, self.Hkv) if self.precise_mma else 16
+            self._tiles = token_tiles(rows, skip_single_token=True)
             key = ("zero_tile_starts", ctx.max_batch_seqs)
             if key not in ctx.shared:
                 ctx.shared[key] = torch.zeros(ctx.max_batch_seqs + 4, dtype=torch.int32, device=ctx.device)
@@ -221,17 +224,23 @@ class GQAAttention(Mixer):
         g = step.groups[cache.group]
         if out is None:
             out = torch.empty((T, self.Hq * self.vd), dtype=self.ctx.dtype, device=q.device)
-        if self.precise_mma:
+        if self.general and self._single is not None:
             (single,) = step.index(self._single)
-            if single.numel():                        # every single token is a tile of one row
+            if single.numel() and self.fast_single:
+                K.attention_single(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single, self.Hq, self.Hkv,
+                                   self.hd, self.scale, self.window, self.block, self.vd)
+            elif single.numel():                      # every single token is a tile of one row
                 K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single,
                                   self._zeros[: single.numel()], self.Hq, self.Hkv, self.hd, self.scale,
                                   self.window, self.block, self.vd)
             tile_entry, tile_tok0 = step.index(self._tiles)
-            if tile_entry.numel():
+            if tile_entry.numel() and self.precise_mma:
                 K.attention_prefill_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry,
                                          tile_tok0, self.Hq, self.Hkv, self.hd, self.scale, self.window,
                                          self.block, precise=True)
+            elif tile_entry.numel():
+                K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
+                                  self.Hq, self.Hkv, self.hd, self.scale, self.window, self.block, self.vd)
             return out
         if not self.use_mma:
             tile_entry, tile_q0 = step.index(self._tiles)

@@ -139,6 +139,7 @@ def test_block_attention_edges(dk, dv):
     keys = unit[:, None, :].repeat(1, G, 1)
     vals = rnd(n, G, dv, seed=1)
     cache = paged(keys, vals, page, table, torch.float32)
+    cache16 = paged(keys, vals, page, table, torch.bfloat16)
     bt = i32([table])
 
     def attend(first, count, targets):
@@ -151,6 +152,13 @@ def test_block_attention_edges(dk, dv):
         K().attention_plain(q.to(DEV), out, cache, bt, i32([0, count]), i32([first + count]), i32([0] * len(tiles)),
                             i32(tiles), H, G, dk, 1.0, None, block, dv)
         return out.cpu().view(count, H, dv)
+
+    def attend_single(pos, tgt):
+        """The kernel for entries of one token (the cache in bf16, as it serves the bfloat16 engine)."""
+        q = (keys[tgt, 0] * gain).repeat(H).view(1, H * dk).to(torch.bfloat16).to(DEV)
+        out = torch.empty((1, H * dv), dtype=torch.bfloat16, device=DEV)
+        K().attention_single(q, out, cache16, bt, i32([0, 1]), i32([pos + 1]), i32([0]), H, G, dk, 1.0, None, block, dv)
+        return out.float().cpu().view(H, dv)
 
     def check(pos, tgt, out_row):
         seen = tgt <= pos and tgt // block == pos // block
@@ -169,6 +177,12 @@ def test_block_attention_edges(dk, dv):
     for p in (19, 20, 21, 39, 40, 41, 59, 60, 74):
         for tgt in {p, p // block * block, max(0, p // block * block - 1), max(0, p - 19), max(0, p - 20)}:
             check(p, tgt, attend(p, 1, [tgt])[0])
+            if K().attention_single_supports(H, G, dk, dv):
+                seen = tgt <= p and tgt // block == p // block
+                got = attend_single(p, tgt)
+                for h in range(H):
+                    close = float((got[h] - vals[tgt, h // (H // G)]).abs().max()) < 3e-2
+                    assert close == seen, (p, tgt, h)
 
 
 @pytest.mark.parametrize("hd,H,G", [(32, 4, 2), (64, 6, 1)])
