@@ -228,11 +228,27 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
             float s[SG];
 #pragma unroll
             for (int g = 0; g < SG; ++g) s[g] = 0.f;
-            for (int d = 0; d < HD; ++d) {
-                const float kd = to_f32<T>(kp[d]);
+            constexpr int VEC = 16 / (int)sizeof(T);         // elements of a 16-byte load
+            if constexpr (HD % VEC == 0) {                   // key rows start on 16-byte boundaries then
+#pragma unroll 4
+                for (int d0 = 0; d0 < HD; d0 += VEC) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(kp + d0);
+                    const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-                for (int g = 0; g < SG; ++g)
-                    if (g < G) s[g] = fmaf(qs[g * HD + d], kd, s[g]);
+                    for (int i = 0; i < VEC; ++i) {
+                        const float kd = to_f32<T>(e[i]);
+#pragma unroll
+                        for (int g = 0; g < SG; ++g)
+                            if (g < G) s[g] = fmaf(qs[g * HD + d0 + i], kd, s[g]);
+                    }
+                }
+            } else {
+                for (int d = 0; d < HD; ++d) {
+                    const float kd = to_f32<T>(kp[d]);
+#pragma unroll
+                    for (int g = 0; g < SG; ++g)
+                        if (g < G) s[g] = fmaf(qs[g * HD + d], kd, s[g]);
+                }
             }
 #pragma unroll
             for (int g = 0; g < SG; ++g)
