@@ -229,7 +229,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 #pragma unroll
             for (int g = 0; g < SG; ++g) s[g] = 0.f;
             constexpr int VEC = 16 / (int)sizeof(T);         // elements of a 16-byte load
-            if constexpr (HD % VEC == 0) {                   // key rows start on 16-byte boundaries then
+            if (HD % VEC == 0 && page_elems % VEC == 0) {    // key rows start on 16-byte boundaries then
 #pragma unroll 4
                 for (int d0 = 0; d0 < HD; d0 += VEC) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(kp + d0);
