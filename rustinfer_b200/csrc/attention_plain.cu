@@ -284,6 +284,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 #pragma unroll
                 for (int i = 0; i < SV; ++i) acc[g][i] *= a;
             }
+#pragma unroll 4                                          // the loads of four keys in flight
         for (int kk = warp; kk < n; kk += WARPS) {
             const int key = k0 + kk, blk = key / page_size;
             const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD;

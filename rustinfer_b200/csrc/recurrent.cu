@@ -158,12 +158,27 @@ __device__ __forceinline__ void store_state(const float (&S)[C][NR], float* sp, 
         }
 }
 
+// The round's values of the CTA's columns: loaded with the round's other vectors (addresses clamped to
+// the tile, as theirs are), stored after them, so that a round costs the loaders one trip to memory.
+constexpr int PERV = (TC * COLS + WORKERS - 1) / WORKERS;
 template <typename TA>
-__device__ __forceinline__ void stage_values(float* vs, const TA* v, int v_stride, int t0, int nt, int h, int dv,
-                                             int c0, int lt) {
-    for (int e = lt; e < nt * COLS; e += WORKERS) {
-        const int tok = e / COLS, c = e - tok * COLS;
-        vs[tok * COLS + c] = c0 + c < dv ? ld(v, (size_t)(t0 + tok) * v_stride + (size_t)h * dv + c0 + c) : 0.f;
+__device__ __forceinline__ void load_values(float (&vv)[PERV], const TA* v, int v_stride, int t0, int nt, int h, int dv,
+                                            int c0, int lt) {
+#pragma unroll
+    for (int j = 0; j < PERV; ++j) {
+        const int e = min(lt + j * WORKERS, nt * COLS - 1);
+        const int tok = e / COLS, c = min(e - tok * COLS, dv - 1 - c0);
+        vv[j] = ld(v, (size_t)(t0 + tok) * v_stride + (size_t)h * dv + c0 + c);
+    }
+}
+__device__ __forceinline__ void store_values(float* vs, const float (&vv)[PERV], int nt, int dv, int c0, int lt) {
+#pragma unroll
+    for (int j = 0; j < PERV; ++j) {
+        const int e = lt + j * WORKERS;
+        if (e < nt * COLS) {
+            const int tok = e / COLS, c = e - tok * COLS;
+            vs[tok * COLS + c] = c0 + c < dv ? vv[j] : 0.f;
+        }
     }
 }
 
@@ -255,6 +270,8 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
     auto stage = [&](int round) {
         const GatedHalf hb(smem + (round & 1) * HALF);
         const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+        float vv[PERV];
+        load_values(vv, v, v_stride, t0, nt, h, dv, c0, lt);
         // every load of the round is issued before the first is used: addresses past the round's
         // end are clamped to its last element (read again, stored nowhere) so that no load is conditional
         if (vec) {
@@ -302,7 +319,7 @@ gated_scan_kernel(const TA* __restrict__ q, int q_stride, const TA* __restrict__
                 }
             }
         }
-        stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
+        store_values(hb.v, vv, nt, dv, c0, lt);
     };
 
     bool ok[C];
@@ -437,6 +454,8 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
     auto stage = [&](int round) {
         const DeltaHalf hb(smem + (round & 1) * HALF);
         const int t0 = t_begin + round * TC, nt = min(TC, t_end - t0);
+        float vv[PERV];
+        load_values(vv, v, v_stride, t0, nt, h, dv, c0, lt);
         if (vec) {                                           // loads unconditional, as in the gated kernel
             float4 rv[PER4], kv[PER4], wv[PER4], uv[PER4], av[PER4];
 #pragma unroll
@@ -490,7 +509,7 @@ delta_scan_kernel(const TA* __restrict__ r, int r_stride, const TA* __restrict__
                 }
             }
         }
-        stage_values(hb.v, v, v_stride, t0, nt, h, dv, c0, lt);
+        store_values(hb.v, vv, nt, dv, c0, lt);
     };
 
     bool ok[C];
