@@ -3,12 +3,13 @@
 config.json names the width, the vocabulary, the norms' eps and a list of layers; every layer
 names its mixer (`type`), the mixer's sizes and constants (`mixer`) and its feed-forward (`mlp`,
 null for none).  Each kind of mixer and feed-forward has a record of its own here, so a size or a
-constant that config.json gives is a field that code reads, and a key the engine does not know is
-an error rather than a silent default.  The rank of a mixer's low-rank decay projection is not in
+constant that config.json gives is a field that code reads; an unknown mixer type or feed-forward kind
+is an error, a key the engine does not know is named in a warning.  The rank of a mixer's low-rank decay projection is not in
 config.json: it is the shape of the tensors (`rank` may be given for random-weights models).
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Any, Dict, Mapping, Optional, Tuple, Union
 
@@ -16,9 +17,11 @@ from .model_config import ConfigError, _eos_ids, _need
 
 
 def _only(d: Mapping[str, Any], known, where: str) -> None:
+    """Keys the engine does not know are named in a warning: they may be notes of whoever wrote the file,
+    and they may be constants of a variant this engine does not compute."""
     extra = sorted(set(d) - set(known))
     if extra:
-        raise ConfigError(f"config.json: {where} has keys the engine does not know: {extra}")
+        warnings.warn(f"config.json: {where} has keys the engine does not know and does not use: {extra}")
 
 
 def _rank(d: Mapping[str, Any]) -> Optional[int]:

@@ -131,10 +131,10 @@ def test_config_registry_and_declared_tensors():
     bad["layers"][1]["mlp"]["kind"] = "experts"
     with pytest.raises(ConfigError):
         resolve_architecture(bad).parse_config(bad, None)
-    bad = config_json("Z")
-    bad["layers"][0]["mixer"]["window"] = 9
-    with pytest.raises(ConfigError):
-        resolve_architecture(bad).parse_config(bad, None)
+    odd = config_json("Z")
+    odd["layers"][0]["mixer"]["note"] = "a key nobody reads"
+    with pytest.warns(UserWarning, match="note"):
+        resolve_architecture(odd).parse_config(odd, None)
 
 
 def test_cache_layout_of_mixed_layers():
