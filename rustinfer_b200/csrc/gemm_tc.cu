@@ -36,16 +36,7 @@ constexpr int BM = 128;                 // rows of the A operand per tile (MMA M
 constexpr int BK = 64;                  // 64 bf16 = one 128-byte swizzle row
 constexpr int THREADS = 192;
 
-// EPI_GELU, EPI_TANH, EPI_GELU_TANH: an activation of every element (fp32: gelu with erf, tanh, gelu with
-// tanh), stored as bf16
-enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_RESIDUAL = 3, EPI_ROPE = 4, EPI_GELU = 5, EPI_TANH = 6,
-                EPI_GELU_TANH = 7 };
-
-__device__ __forceinline__ float activate(int epilogue, float z) {
-    if (epilogue == EPI_GELU) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
-    if (epilogue == EPI_TANH) return tanhf(z);
-    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-}
+enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_RESIDUAL = 3, EPI_ROPE = 4 };
 enum ErrorCode { ERR_PRODUCER_WAIT = 1, ERR_MMA_WAIT = 2, ERR_EPILOGUE_WAIT = 3, ERR_DRAIN_WAIT = 4 };
 
 
@@ -109,9 +100,6 @@ __device__ __forceinline__ void store_one(const Params& p, int n_tok, int n_feat
     const size_t row = (size_t)tok * p.ld_out;
     switch (p.epilogue) {
         case EPI_BF16: reinterpret_cast<bf16*>(p.out)[row + feat] = __float2bfloat16_rn(acc); break;
-        case EPI_GELU: case EPI_TANH: case EPI_GELU_TANH:
-            reinterpret_cast<bf16*>(p.out)[row + feat] = __float2bfloat16_rn(activate(p.epilogue, acc));
-            break;
         case EPI_F32: reinterpret_cast<float*>(p.out)[row + feat] = acc; break;
         case EPI_RESIDUAL: atomicAdd(reinterpret_cast<float*>(p.out) + row + feat, acc); break;   // parts of one sum may come from several CTAs
         case EPI_SILU:                                   // even feature = gate_j, odd = up_j
@@ -136,15 +124,6 @@ __device__ __forceinline__ void store_row16(const Params& p, int tok, int feat0,
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
             dst[0] = pack8(v);
             dst[1] = pack8(v + 8);
-            break;
-        }
-        case EPI_GELU: case EPI_TANH: case EPI_GELU_TANH: {
-            float a[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) a[j] = activate(p.epilogue, v[j]);
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
-            dst[0] = pack8(a);
-            dst[1] = pack8(a + 8);
             break;
         }
         case EPI_F32: {
@@ -185,17 +164,6 @@ __device__ __forceinline__ void store_row64(const Params& p, int tok, int feat0,
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
 #pragma unroll
             for (int j = 0; j < 8; ++j) dst[j] = pack8(v + 8 * j);
-            break;
-        }
-        case EPI_GELU: case EPI_TANH: case EPI_GELU_TANH: {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float a[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) a[i] = activate(p.epilogue, v[8 * j + i]);
-                dst[j] = pack8(a);
-            }
             break;
         }
         case EPI_F32: {
@@ -965,7 +933,7 @@ int gemm_tc_impl(const void* X, const void* W, int M, int N, int K, void* out, i
     p.tiles_a = (p.a_rows + BM - 1) / BM;
     const int tiles_b = (p.b_rows + bn - 1) / bn;
     p.n_tiles = p.tiles_a * tiles_b;
-    const int esize = (epilogue == EPI_BF16 || epilogue == EPI_SILU || epilogue >= EPI_GELU) ? 2 : 4;
+    const int esize = (epilogue == EPI_BF16 || epilogue == EPI_SILU) ? 2 : 4;
     p.vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && ((size_t)ld_out * esize) % 16 == 0) ? 1 : 0;
     CUtensorMap ma, mb;
     p.a_box = a_box;

@@ -123,7 +123,6 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 # ------------------------------------------------------------ tcgen05 bf16 matrix product
 EPI_BF16, EPI_F32, EPI_SILU, EPI_RESIDUAL = 0, 1, 2, 3
-EPI_GELU, EPI_TANH, EPI_GELU_TANH = 5, 6, 7            # an activation of every element (fp32), stored as bf16
 _tc_state = {}
 _TC_WORKSPACE_FLOATS = 8 << 20
 _TC_COUNTERS = 1 << 14
@@ -191,7 +190,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
     """out = x[M,K] @ w[N,K]^T on the tcgen05 tensor cores, bf16 inputs, fp32 accumulation.
     epilogue: EPI_BF16 / EPI_F32 store into out [M,N]; EPI_SILU stores silu(gate)*up into
     out [M,N/2] for a weight whose rows alternate gate_j, up_j; EPI_RESIDUAL adds into the
-    fp32 out [M,N]; EPI_GELU (with erf), EPI_TANH, EPI_GELU_TANH store the activation of every element as bf16."""
+    fp32 out [M,N]."""
     require_cuda(x, w, out)
     if not gemm_tc_supports(x, w):
         raise KernelError("gemm_tc: contiguous, 16-byte aligned bfloat16 x [M,K] and w [N,K] with K a multiple of 8")
@@ -200,7 +199,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
     if w.shape[1] != Kd or out.stride(1) != 1:
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     cols = N // 2 if epilogue == EPI_SILU else N
-    want = torch.bfloat16 if epilogue in (EPI_BF16, EPI_SILU, EPI_GELU, EPI_TANH, EPI_GELU_TANH) else torch.float32
+    want = torch.bfloat16 if epilogue in (EPI_BF16, EPI_SILU) else torch.float32
     if out.dtype != want or out.shape != (M, cols) or (epilogue == EPI_SILU and N % 2):
         raise KernelError(f"gemm_tc: out must be {want} [{M}, {cols}] for epilogue {epilogue}")
     plan = plan or gemm_tc_plan(M, N, Kd, num_sms, epilogue)

@@ -58,16 +58,13 @@ class SwiGLU(FeedForward):
 
 
 _ACTIVATIONS = {"gelu": K.ACT_GELU_ERF, "gelu_erf": K.ACT_GELU_ERF, "tanh": K.ACT_TANH, "gelu_tanh": K.ACT_GELU_TANH}
-# the same activations as epilogues of the tensor-core product
-_EPILOGUES = {K.ACT_GELU_ERF: K.EPI_GELU, K.ACT_TANH: K.EPI_TANH, K.ACT_GELU_TANH: K.EPI_GELU_TANH}
 
 
 @register_feed_forward("dense_mlp")
 class DenseMLP(FeedForward):
     """down( act(up(x)) ) without a gate.  params: hidden_size, intermediate_size, activation
     ("gelu": with erf; "gelu_tanh"; "tanh"), up_name / down_name (tensor names, default
-    "up_proj.weight" / "down_proj.weight").  The activation is computed in fp32, in the bfloat16 engine
-    inside the up product's epilogue (from the fp32 accumulator: one rounding instead of two)."""
+    "up_proj.weight" / "down_proj.weight").  The activation is computed in fp32."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -91,10 +88,8 @@ class DenseMLP(FeedForward):
         self.down = Linear(tensors[self.down_name], self.ctx.num_sms)
 
     def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None):
-        u = self.up.activated(x, _EPILOGUES[self.act]) if self.ctx.dtype == torch.bfloat16 else None
-        if u is None:                                     # 32-bit, or a weight the tensor-core product does not take
-            u = self.up(x, out_dtype=self.ctx.dtype)
-            K.activation(u, u, self.act)
+        u = self.up(x, out_dtype=self.ctx.dtype)
+        K.activation(u, u, self.act)
         if residual is not None and self.down.add_into(u, residual):
             return None
         return self.down(u, out_dtype=self.ctx.dtype)

@@ -58,16 +58,6 @@ class Linear:
         K.gemm_tc(x, self.weight, residual, K.EPI_RESIDUAL, num_sms=self.num_sms)
         return True
 
-    def activated(self, x: torch.Tensor, epilogue: int) -> Optional[torch.Tensor]:
-        """act(x W^T) as bf16 with the activation in the product's epilogue (`epilogue`: K.EPI_GELU, K.EPI_TANH
-        or K.EPI_GELU_TANH); None if this weight cannot take that path (the caller then runs the product and
-        the activation one after the other)."""
-        if not self._own(x):
-            return None
-        out = torch.empty((x.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
-        K.gemm_tc(x, self.weight, out, epilogue, num_sms=self.num_sms)
-        return out
-
     def silu_pairs(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """For a weight whose rows alternate gate_j, up_j: silu(gate) * up, [M, out/2], fused
         into the product's epilogue; None if this weight cannot take that path."""

@@ -167,10 +167,8 @@ class DeltaRule(_StateMixer):
     def forward(self, x: torch.Tensor, step: StepContext, cache: StateLayerCache) -> torch.Tensor:
         T, dt = x.shape[0], self.ctx.dtype
         p = self._split(self.proj(x, out_dtype=dt))
-        low = self.w1.activated(x, K.EPI_TANH) if dt == torch.bfloat16 else None
-        if low is None:
-            low = self.w1(x, out_dtype=dt)
-            K.activation(low, low, K.ACT_TANH)
+        low = self.w1(x, out_dtype=dt)
+        K.activation(low, low, K.ACT_TANH)
         zw = self.w2(low, out_dtype=torch.float32)
         o = torch.empty((T, self.H * self.dk), dtype=torch.float32, device=x.device)
         K.delta_scan(p["r"], p["k"], p["v"], p["a"], self.a_bias, zw, self.w_bias, self.decay_rate, self.unit_eps,

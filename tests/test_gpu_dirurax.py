@@ -92,22 +92,6 @@ def test_activations_and_scaled_sum():
     assert float((out.cpu().to(F64) - (0.6 * x.cpu().to(F64) - 1.7 * y.cpu().to(F64))).abs().max()) < 1e-6
 
 
-@pytest.mark.parametrize("M,N,Kd", [(5, 40, 64), (70, 136, 96), (600, 264, 128), (1100, 1024, 256)])
-def test_product_with_an_activation_in_its_epilogue(M, N, Kd):
-    """The tensor-core product's activation epilogues (few tokens, many tokens on one CTA, many on CTA pairs;
-    feature counts that are no multiple of a tile) against the product and the activation in float64."""
-    x = rnd(M, Kd, seed=1).to(torch.bfloat16)
-    w = (rnd(N, Kd, seed=2) / math.sqrt(Kd) * 2).to(torch.bfloat16)
-    z = x.to(F64) @ w.to(F64).T
-    refs = {K().EPI_GELU: P.gelu_erf(z), K().EPI_TANH: torch.tanh(z),
-            K().EPI_GELU_TANH: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))}
-    for epi, ref in refs.items():
-        out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
-        K().gemm_tc(x.to(DEV), w.to(DEV), out, epi)
-        torch.cuda.synchronize()
-        assert float((out.cpu().to(F64) - ref).abs().max()) <= 2.0 ** -8 * max(1.0, float(ref.abs().max())) * 1.05, epi
-
-
 @pytest.mark.parametrize("per_head", [False, True])
 def test_gated_head_norm(per_head):
     T, H, dv, eps = 6, 3, 20, 1e-4
