@@ -91,6 +91,107 @@ __global__ void sandwich_norm_kernel(float* __restrict__ h, const TA* __restrict
         op[i] = from_f32<TA>((row[i] - mean) * inv * wval(next_w, i, 1.f) + wval(next_b, i, 0.f));
 }
 
+// The same for bf16 activations and rows of a multiple of 8 up to 8 * 1024 elements: a thread keeps its 8
+// elements in registers from the first load to the last store and moves 16 or 32 bytes per access.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(p[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+template <typename TW>
+__device__ __forceinline__ void weights8(const TW* w, int i0, float dflt, float (&f)[8]) {
+    if (!w) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = dflt;
+    } else if (sizeof(TW) == 2) {
+        unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(w) + i0), f);
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i0);
+        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i0 + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+}
+// mean and 1 / sqrt(variance + eps) of a row spread over the block, 8 elements a thread (two passes)
+__device__ __forceinline__ void row_stats(const float (&v)[8], bool active, float inv_d, float eps, float* red,
+                                          float& mean, float& inv) {
+    float s = 0.f;
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += v[i];
+    }
+    mean = block_sum(s, red) * inv_d;
+    float q = 0.f;
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q += (v[i] - mean) * (v[i] - mean);
+    }
+    inv = 1.0f / sqrtf(block_sum(q, red) * inv_d + eps);
+}
+
+template <typename TW>
+__global__ void sandwich_norm_bf16x8_kernel(float* __restrict__ h, const bf16* __restrict__ delta,
+                                            const TW* __restrict__ post_w, const TW* __restrict__ post_b,
+                                            const TW* __restrict__ next_w, const TW* __restrict__ next_b,
+                                            bf16* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const int i0 = threadIdx.x * 8;
+    const bool active = i0 < d;
+    const float inv_d = 1.0f / (float)d;
+    float* hp = h + (size_t)src * d + i0;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (active) {
+        const float4 a = *reinterpret_cast<const float4*>(hp);
+        const float4 b = *reinterpret_cast<const float4*>(hp + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    if (delta) {
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = 0.f;
+        if (active) unpack8(*reinterpret_cast<const uint4*>(delta + (size_t)src * d + i0), x);
+        float mean, inv;
+        row_stats(x, active, inv_d, eps, red, mean, inv);
+        if (active) {
+            float w[8], b[8];
+            weights8(post_w, i0, 1.f, w);
+            weights8(post_b, i0, 0.f, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] += (x[i] - mean) * inv * w[i] + b[i];
+            if (!rows) {
+                *reinterpret_cast<float4*>(hp) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(hp + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        }
+    }
+    if (!out) return;
+    float mean, inv;
+    row_stats(v, active, inv_d, eps, red, mean, inv);
+    if (!active) return;
+    float w[8], b[8], y[8];
+    weights8(next_w, i0, 1.f, w);
+    weights8(next_b, i0, 0.f, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = (v[i] - mean) * inv * w[i] + b[i];
+    *reinterpret_cast<uint4*>(out + (size_t)r * d + i0) = pack8(y);
+}
+
 // ----------------------------------------- per-head norms of q, k, v + write into the pages
 // qkv row: q heads [Hq][dk], k heads [Hkv][dk], v heads [Hkv][dv].  One warp per (token, head):
 // q and k are divided by their root mean square over dk and multiplied by a weight of size dk
@@ -299,6 +400,20 @@ RI_API int ri_sandwich_norm(float* h, const void* delta, const void* post_w, con
     if (n_rows <= 0) return 0;
     if ((size_t)d * sizeof(float) > 200 * 1024) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
+    const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (act_dtype == RI_BF16 && d % 8 == 0 && d <= 8 * 1024 && aligned(h) && aligned(delta) && aligned(out) &&
+        aligned(post_w) && aligned(post_b) && aligned(next_w) && aligned(next_b)) {
+        const int threads = ((d / 8 + 31) / 32) * 32;
+        if (w_dtype == RI_BF16)
+            RI_CHECKED(ri_launch(sandwich_norm_bf16x8_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, h, (const bf16*)delta,
+                                 (const bf16*)post_w, (const bf16*)post_b, (const bf16*)next_w, (const bf16*)next_b,
+                                 (bf16*)out, rows, d, eps));
+        else
+            RI_CHECKED(ri_launch(sandwich_norm_bf16x8_kernel<float>, dim3(n_rows), dim3(threads), 0, s, h, (const bf16*)delta,
+                                 (const float*)post_w, (const float*)post_b, (const float*)next_w, (const float*)next_b,
+                                 (bf16*)out, rows, d, eps));
+        return ri_launch_status();
+    }
     if (act_dtype == RI_BF16 && w_dtype == RI_BF16)
         return sandwich_norm_launch<bf16, bf16>(h, delta, post_w, post_b, next_w, next_b, out, rows, n_rows, d, eps, s);
     if (act_dtype == RI_BF16)
