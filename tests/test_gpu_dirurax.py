@@ -353,6 +353,39 @@ def test_gated_scan_keeps_a_far_key():
     assert float((o[-1].cpu().to(F64) - want).abs().max()) < 1e-4
 
 
+def test_delta_scan_keeps_and_overwrites():
+    """Decay one and removal rate zero: the state only gathers k v^T, and a key written 500 tokens back is read
+    by a single token.  Removal rate one: writing a unit key again replaces what it pointed at."""
+    d, T = 16, 500
+    k = torch.zeros(T + 1, d)
+    for t in range(T):
+        k[t, t % d] = 1.0
+    v = rnd(T + 1, d, seed=1)
+    r = torch.zeros(T + 1, d)
+    r[T, 3] = 1.0
+    k[T] = 0
+    hold = torch.full((T + 1, d), -40.0)                               # sigmoid(-40) = 0: decay exp(0) = 1, rate 0
+    state = torch.zeros((1, 1, d, K().recurrent_state_rows(d)), device=DEV)
+    at = 0
+    for n in (63, 2, 300, 135, 1):
+        o = torch.empty((n, d), dtype=torch.float32, device=DEV)
+        x = torch.cat([r[at: at + n], k[at: at + n], v[at: at + n], hold[at: at + n]], dim=1).to(DEV)
+        K().delta_scan(x[:, :d], x[:, d: 2 * d], x[:, 2 * d: 3 * d], x[:, 3 * d:], None, hold[at: at + n].clone().to(DEV), None,
+                       math.exp(-0.5), 1e-6, o, state, i32([0, n]), i32([0]), 1, 1, d, d)
+        at += n
+    assert float((o[-1].cpu().to(F64) - v[3:T:d].to(F64).sum(0)).abs().max()) < 1e-4
+    # removal rate one (logit +40), no decay: key e_5 written twice, read once
+    state.zero_()
+    k2 = torch.zeros(3, d); k2[0, 5] = 1.0; k2[1, 5] = 1.0
+    r2 = torch.zeros(3, d); r2[2, 5] = 1.0
+    v2 = rnd(3, d, seed=2)
+    o = torch.empty((3, d), dtype=torch.float32, device=DEV)
+    x = torch.cat([r2, k2, v2, torch.full((3, d), 40.0)], dim=1).to(DEV)
+    K().delta_scan(x[:, :d], x[:, d: 2 * d], x[:, 2 * d: 3 * d], x[:, 3 * d:], None, torch.full((3, d), -40.0, device=DEV), None,
+                   math.exp(-0.5), 1e-6, o, state, i32([0, 3]), i32([0]), 1, 1, d, d)
+    assert float((o[2].cpu() - v2[1]).abs().max()) < 1e-4
+
+
 # ============================================================================ the engine
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
