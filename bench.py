@@ -17,7 +17,9 @@ attention), the Llama-3.2-3B-shaped model at 8 of its 28 layers serving 64 reque
 this engine's attention and GEMM kernels timed against the reference's own attention kernels
 (compiled unmodified, see baseline/reference_kernels.py) and the library GEMM on the same data.
 `--shape` takes the layer sizes of the 3B or 8B benchmark configuration for the headline instead;
-`--only decode|prefill|serve` runs one part alone and prints its time.
+`--only decode|prefill|serve` runs one part alone and prints its time.  `--family dirurax` leaves all of that
+aside and prints a line of its own: prefill and decode of Dirurax models at two sizes beside Llama models of the
+same width, depth, feed-forward width and vocabulary, and that family's kernels alone against their rooflines.
 """
 from __future__ import annotations
 
