@@ -121,7 +121,7 @@ def test_config_registry_and_declared_tensors():
             assert all(a == b or a == -1 for a, b in zip(decls[n].shape, shape)), n
     bad = config_json("X")
     bad["layers"][0]["mixer"]["left"]["mask"] = {"span": 3}
-    with pytest.raises(ConfigError):
+    with pytest.raises(ConfigError), pytest.warns(UserWarning, match="span"):
         resolve_architecture(bad).parse_config(bad, None)
     bad = config_json("X")
     bad["layers"][1]["type"] = "mamba"
