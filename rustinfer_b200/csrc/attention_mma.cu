@@ -125,7 +125,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                const int* __restrict__ tile_entry, const int* __restrict__ tile_tok0,
                int Hq, int Hkv, int Gc, int chunks, int tpt, int page_size, float scale_log2, int window,
-               int block) {
+               int block, int sink) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -190,6 +190,12 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
 #pragma unroll
     for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (sink) {
+        // a key of score 0 without a value: maximum 0 and, in the one lane of four whose partial sum
+        // stands for it, a weight of 2^(0 - 0) = 1
+        m[0] = m[1] = 0.f;
+        if ((lane & 3) == 0) l[0] = l[1] = 1.f;
+    }
 
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
@@ -929,7 +935,7 @@ RI_API int ri_attention_prefill_bf16(const void* q, int q_stride, void* out, int
                                      const void* cache, const int* block_table, int table_stride,
                                      const int* cu_q, const int* kv_len, const int* tile_entry,
                                      const int* tile_tok0, int n_tiles, int Hq, int Hkv, int page_size,
-                                     float scale, int window, int block, int precise, void* stream) {
+                                     float scale, int window, int block, int precise, int sink, void* stream) {
     if (n_tiles <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
     int st = configure();
@@ -940,12 +946,12 @@ RI_API int ri_attention_prefill_bf16(const void* q, int q_stride, void* out, int
         RI_CHECKED(ri_launch(prefill_kernel<true>, dim3(grid), dim3(THREADS), PREFILL_SMEM, (cudaStream_t)stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
             cu_q, kv_len, tile_entry, tile_tok0, Hq, Hkv, Gc, chunks, tpt, page_size,
-            scale * 1.4426950408889634f, window, block));
+            scale * 1.4426950408889634f, window, block, sink));
     else
         RI_CHECKED(ri_launch(prefill_kernel<false>, dim3(grid), dim3(THREADS), PREFILL_SMEM, (cudaStream_t)stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
             cu_q, kv_len, tile_entry, tile_tok0, Hq, Hkv, Gc, chunks, tpt, page_size,
-            scale * 1.4426950408889634f, window, block));
+            scale * 1.4426950408889634f, window, block, sink));
     return ri_launch_status();
 }
 

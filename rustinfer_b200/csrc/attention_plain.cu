@@ -43,7 +43,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const T* __restrict__ cache, const int* __restrict__ block_table,
                        int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                        const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
-                       int Hq, int Hkv, int page_size, float scale, int window, int block) {
+                       int Hq, int Hkv, int page_size, float scale, int window, int block, int sink) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -81,7 +81,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
         lo_tile = max(lo_tile, ((pos0 + j0) / block) * block);
     }
 
-    float m = -INFINITY, l = 0.f;
+    // with a sink the sums start from a key of score 0 that has no value: maximum 0, sum exp(0 - 0) = 1
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
@@ -185,7 +186,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
                         const T* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                         const int* __restrict__ entry_list, int Hq, int Hkv, int page_size, float scale,
-                        int window, int block) {
+                        int window, int block, int sink) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -208,7 +209,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     constexpr int WARPS = THREADS / 32;
     for (int e = tid; e < G * HD; e += THREADS)
         qs[e] = to_f32<T>(q[(size_t)t * q_stride + (size_t)kvh * G * HD + e]);
-    if (tid < G) { mrun[tid] = -INFINITY; lrun[tid] = 0.f; }
+    if (tid < G) { mrun[tid] = sink ? 0.f : -INFINITY; lrun[tid] = sink ? 1.f : 0.f; }
     float acc[SG][SV];
 #pragma unroll
     for (int g = 0; g < SG; ++g)
@@ -322,7 +323,7 @@ template <typename T>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* cache,
            const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
            const int* tile_entry, const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
-           float scale, int window, int block, cudaStream_t s) {
+           float scale, int window, int block, int sink, cudaStream_t s) {
     static bool configured = false;
     const size_t smem = SMEM_FLOATS * sizeof(float);
     if (!configured) {
@@ -334,7 +335,7 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* c
     dim3 grid(n_tiles, Hq);
     RI_CHECKED(ri_launch(attention_plain_kernel<T>, dim3(grid), dim3(THREADS), smem, s, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)cache, block_table, table_stride,
-        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window, block));
+        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window, block, sink));
     return ri_launch_status();
 }
 }  // namespace
@@ -346,20 +347,21 @@ RI_API int ri_attention_plain_tile_rows() { return QT; }
 // q: rows of `q_stride` elements, head h at column h*HD; out rows of out_stride, head h at
 // column h*VD.  cache: one layer, per page the keys [kv head][slot][HD] and then the values
 // [kv head][slot][VD] ([page][K|V][kv head][slot][HD] when the two sizes are equal).  tile_entry[i] = batch entry of tile i
-// (-1: skip), tile_q0[i] = its first query row within that entry.
+// (-1: skip), tile_q0[i] = its first query row within that entry.  sink: the softmax's denominator has one
+// added, p_j = exp(s_j) / (1 + sum exp(s_j)): a key of score 0 that carries no value.
 RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_stride,
                               const void* cache, int dtype, const int* block_table, int table_stride,
                               const int* cu_q, const int* kv_len, const int* tile_entry,
                               const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
-                              float scale, int window, int block, void* stream) {
+                              float scale, int window, int block, int sink, void* stream) {
     if (n_tiles <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RI_BF16)
         return launch<bf16>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
-                            kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, s);
+                            kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink, s);
     return launch<float>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
-                         kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, s);
+                         kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink, s);
 }
 
 // Entries that bring a single token (entry_list[i], -1: skip): keys and values of a kv head are read once
@@ -368,7 +370,7 @@ RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_st
 RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_stride, const void* cache, int dtype,
                                const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                const int* entry_list, int n_entries, int Hq, int Hkv, int page_size, float scale,
-                               int window, int block, void* stream) {
+                               int window, int block, int sink, void* stream) {
     if (n_entries <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
     if (Hq / Hkv > SG || SV > 4) return (int)cudaErrorNotSupported;
@@ -382,7 +384,7 @@ RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_s
         configured = true; } \
     RI_CHECKED(ri_launch(attention_single_kernel<T>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (T*)out, \
         out_stride, (const T*)cache, block_table, table_stride, cu_q, kv_len, entry_list, Hq, Hkv, page_size, scale, \
-        window, block)); } while (0)
+        window, block, sink)); } while (0)
     if (dtype == RI_BF16) RI_SINGLE(bf16);
     else RI_SINGLE(float);
 #undef RI_SINGLE

@@ -1,0 +1,312 @@
+// A feed-forward of routed experts: the router's choice, the sort of (token, choice) pairs by expert,
+// the experts' products over the sorted rows, and the weighted sum back per token.  Nothing here reads a
+// count on the host: every launch has a grid that covers the worst case and finds its work in the offsets
+// the sort left on the device, so a step of these kernels can be captured in a CUDA graph.
+//
+//   route    z [T][E] fp32 router logits -> ids [T][top], weights [T][top] fp32, counts[e] += 1
+//   sort     ids, counts -> offsets [E+1], order [T*top] (pairs in expert order, stable), place [T*top]
+//   products rows of an expert times that expert's matrix (fp32 sums in a fixed order of k)
+//   combine  y[t] = sum_j weight[t][j] * Y[place[t*top + j]] (+ shared[t]); counts put back to zero
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------------------- router
+// One warp a token.  score s = sigmoid(z); choice c = s + correction.  With groups: the experts form
+// n_groups equal groups of neighbours, a group's score is the sum of its two largest c, and only
+// experts of the `keep` best groups can be chosen (the others count as -inf).  The `top` largest c are
+// chosen, the lowest index among equals; their weights are the s (divided by their sum when renorm).
+__device__ __forceinline__ void warp_argmax(float& v, int& idx) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int T, int E,
+                                 int top, int n_groups, int keep, int renorm, int* __restrict__ ids,
+                                 float* __restrict__ weights, int* __restrict__ counts) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * warps + warp;
+    if (t >= T) return;
+    float* s = sm + (size_t)warp * (2 * E + n_groups);     // [E] scores
+    float* c = s + E;                                      // [E] choice scores
+    float* gs = c + E;                                     // [n_groups] group scores
+    for (int e = lane; e < E; e += 32) {
+        const float sc = 1.0f / (1.0f + expf(-z[(size_t)t * E + e]));
+        s[e] = sc;
+        c[e] = sc + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (n_groups > 0 && keep < n_groups) {
+        const int per = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;            // the two largest
+            for (int i = 0; i < per; ++i) {
+                const float v = c[g * per + i];
+                if (v > a) { b = a; a = v; } else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the `keep` best groups get +inf as a mark, one by one
+        for (int r = 0; r < keep; ++r) {
+            float best = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gs[g];
+                if (v != INFINITY && (v > best || bi == 0x7fffffff)) { best = v; bi = g; }
+            }
+            warp_argmax(best, bi);
+            if (lane == 0 && bi != 0x7fffffff) gs[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    float wsum = 0.f;
+    for (int r = 0; r < top; ++r) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = c[e];
+            if (!isnan(v) && (v > best || (bi == 0x7fffffff && v > -INFINITY))) { best = v; bi = e; }
+        }
+        warp_argmax(best, bi);
+        if (bi == 0x7fffffff) bi = 0;                      // nothing left to choose (the host rules this out)
+        if (lane == 0) {
+            ids[(size_t)t * top + r] = bi;
+            weights[(size_t)t * top + r] = s[bi];
+            atomicAdd(counts + bi, 1);
+            c[bi] = NAN;                                   // taken
+        }
+        wsum += s[bi];
+        __syncwarp();
+    }
+    if (renorm && lane < top) weights[(size_t)t * top + lane] /= wsum;
+}
+
+// --------------------------------------------------------------------------------- sort
+// CTA e: offset of expert e = counts of the experts before it; then the pairs that chose e, in their
+// order of (token, choice), get the places offset, offset + 1, ...
+__global__ void moe_sort_kernel(const int* __restrict__ ids, const int* __restrict__ counts, int N, int E,
+                                int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ place) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ int red[33];
+    __shared__ int wtot[32];
+    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    int part = 0;
+    for (int i = tid; i < e; i += blockDim.x) part += counts[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) red[warp] = part;
+    __syncthreads();
+    if (tid == 0) {
+        int tot = 0;
+        for (int w = 0; w < warps; ++w) tot += red[w];
+        red[32] = tot;
+        offsets[e] = tot;
+        if (e == E - 1) offsets[E] = tot + counts[e];
+    }
+    __syncthreads();
+    int at = red[32];
+    for (int base = 0; base < N; base += blockDim.x) {
+        const int i = base + tid;
+        const bool mine = i < N && ids[i] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) wtot[warp] = __popc(ballot);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < warps; ++w) {
+            if (w < warp) before += wtot[w];
+            total += wtot[w];
+        }
+        if (mine) {
+            const int p = at + before + __popc(ballot & ((1u << lane) - 1u));
+            order[p] = i;
+            place[i] = p;
+        }
+        at += total;
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------------ experts' products
+// Rows in expert order: row p of the product belongs to expert e with offsets[e] <= p < offsets[e+1].
+// A [.., K]: row of place p is a[order[p] / top] when `gather`, else a[p].  W [E][Ntot][K].
+//   GATED: Ntot = 2 N, out[p][n] = silu(A.W[e][n]) * (A.W[e][N + n])   (n < N)
+//   else:  Ntot = N,   out[p][n] = A.W[e][n]
+// Every sum runs over k = 0, 1, .. in that order with fp32 multiply-adds, so an output does not depend on
+// which rows share its tile.  A CTA of 256 threads owns BM x BN outputs of one expert; the grid's x covers
+// ceil(rows / BM) + E tiles (no expert's count is known to the host) and a CTA beyond the last tile returns.
+constexpr int GBN = 64, GBK = 32;
+
+template <typename TA, typename TW, typename TO, int BM, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict__ w, TO* __restrict__ out,
+                   int out_stride, const int* __restrict__ offsets, const int* __restrict__ order, int top,
+                   int gather, int E, int N, int K) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int RM = BM / 16;                            // rows a thread: 16 thread rows
+    constexpr int RN = GBN / 16;                           // columns a thread: 16 thread columns
+    __shared__ float As[BM][GBK + 1];
+    __shared__ float Ws[GATED ? 2 : 1][GBN][GBK + 1];
+    __shared__ int s_tile[3];                              // expert, first row, rows
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, e = 0, row0 = 0, n_rows = 0;
+        for (; e < E; ++e) {
+            const int lo = offsets[e], cnt = offsets[e + 1] - lo;
+            const int tiles = (cnt + BM - 1) / BM;
+            if (tile < tiles) { row0 = lo + tile * BM; n_rows = min(BM, cnt - tile * BM); break; }
+            tile -= tiles;
+        }
+        s_tile[0] = e; s_tile[1] = row0; s_tile[2] = n_rows;
+    }
+    __syncthreads();
+    const int e = s_tile[0], row0 = s_tile[1], n_rows = s_tile[2];
+    if (e >= E || n_rows <= 0) return;
+    const int n0 = blockIdx.y * GBN;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int Ntot = GATED ? 2 * N : N;
+    const TW* we = w + (size_t)e * Ntot * K;
+    float acc[GATED ? 2 : 1][RM][RN];
+#pragma unroll
+    for (int h = 0; h < (GATED ? 2 : 1); ++h)
+#pragma unroll
+        for (int i = 0; i < RM; ++i)
+#pragma unroll
+            for (int j = 0; j < RN; ++j) acc[h][i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += GBK) {
+        for (int idx = tid; idx < BM * GBK; idx += 256) {
+            const int r = idx / GBK, kk = idx - r * GBK;
+            float v = 0.f;
+            if (r < n_rows && k0 + kk < K) {
+                const int p = row0 + r;
+                const int src = gather ? order[p] / top : p;
+                v = to_f32<TA>(a[(size_t)src * a_stride + k0 + kk]);
+            }
+            As[r][kk] = v;
+        }
+        for (int idx = tid; idx < GBN * GBK; idx += 256) {
+            const int c = idx / GBK, kk = idx - c * GBK;
+            const bool ok = n0 + c < N && k0 + kk < K;
+            Ws[0][c][kk] = ok ? to_f32<TW>(we[(size_t)(n0 + c) * K + k0 + kk]) : 0.f;
+            if (GATED) Ws[1][c][kk] = ok ? to_f32<TW>(we[(size_t)(N + n0 + c) * K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < GBK; ++kk) {
+            float av[RM];
+#pragma unroll
+            for (int i = 0; i < RM; ++i) av[i] = As[ty + 16 * i][kk];
+#pragma unroll
+            for (int h = 0; h < (GATED ? 2 : 1); ++h)
+#pragma unroll
+                for (int j = 0; j < RN; ++j) {
+                    const float bv = Ws[h][tx + 16 * j][kk];
+#pragma unroll
+                    for (int i = 0; i < RM; ++i) acc[h][i][j] = fmaf(av[i], bv, acc[h][i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+        const int r = ty + 16 * i;
+        if (r >= n_rows) continue;
+#pragma unroll
+        for (int j = 0; j < RN; ++j) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= N) continue;
+            float v = acc[0][i][j];
+            if (GATED) v = v / (1.0f + expf(-v)) * acc[1][i][j];
+            out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------ combine
+// out[t][c] = sum_j weights[t][j] * Y[place[t*top + j]][c] (+ shared[t][c]), j = 0, 1, .. in that order.
+template <typename TS, typename TO>
+__global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __restrict__ place,
+                                   const float* __restrict__ weights, const TS* __restrict__ shared, TO* __restrict__ out,
+                                   int top, int d, int* __restrict__ counts, int E) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (t == 0)
+        for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;     // ready for the next step
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j)
+            acc = fmaf(weights[(size_t)t * top + j], Y[(size_t)place[(size_t)t * top + j] * d + c], acc);
+        if (shared) acc += to_f32<TS>(shared[(size_t)t * d + c]);
+        out[(size_t)t * d + c] = from_f32<TO>(acc);
+    }
+}
+
+}  // namespace
+
+RI_API int ri_moe_route(const float* z, const float* correction, int T, int E, int top, int n_groups, int keep,
+                        int renorm, int* ids, float* weights, int* counts, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || top > 32 || (n_groups > 0 && (E % n_groups || keep <= 0 || keep > n_groups)))
+        return (int)cudaErrorInvalidValue;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * (2 * E + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    RI_CHECKED(ri_launch(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, (cudaStream_t)stream,
+                         z, correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts));
+    return ri_launch_status();
+}
+
+RI_API int ri_moe_sort(const int* ids, const int* counts, int N, int E, int* offsets, int* order, int* place, void* stream) {
+    if (N <= 0) return 0;
+    RI_CHECKED(ri_launch(moe_sort_kernel, dim3(E), dim3(256), 0, (cudaStream_t)stream, ids, counts, N, E, offsets, order, place));
+    return ri_launch_status();
+}
+
+RI_API int ri_moe_product_rows(int rows, int E) { return rows / E >= 24 ? 64 : 16; }
+
+// a_dtype / w_dtype / out_dtype: RI_F32 or RI_BF16.  rows: T * top (the pairs).  gated: see the kernel.
+RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* w, int w_dtype, void* out, int out_dtype,
+                          int out_stride, const int* offsets, const int* order, int top, int gather, int rows, int E,
+                          int N, int K, int gated, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int bm = ri_moe_product_rows(rows, E);
+    const dim3 grid((rows + bm - 1) / bm + E, (N + GBN - 1) / GBN);
+#define RI_MP(TA, TW, TO, BM, G) RI_CHECKED(ri_launch(moe_product_kernel<TA, TW, TO, BM, G>, grid, dim3(256), 0, s, (const TA*)a, \
+        a_stride, (const TW*)w, (TO*)out, out_stride, offsets, order, top, gather, E, N, K))
+#define RI_MP_BM(TA, TW, TO, G) do { if (bm == 64) RI_MP(TA, TW, TO, 64, G); else RI_MP(TA, TW, TO, 16, G); } while (0)
+    if (a_dtype == RI_BF16 && w_dtype == RI_BF16 && out_dtype == RI_BF16 && gated) RI_MP_BM(bf16, bf16, bf16, true);
+    else if (a_dtype == RI_BF16 && w_dtype == RI_BF16 && out_dtype == RI_F32 && !gated) RI_MP_BM(bf16, bf16, float, false);
+    else if (a_dtype == RI_F32 && w_dtype == RI_F32 && out_dtype == RI_F32 && gated) RI_MP_BM(float, float, float, true);
+    else if (a_dtype == RI_F32 && w_dtype == RI_F32 && out_dtype == RI_F32 && !gated) RI_MP_BM(float, float, float, false);
+    else return (int)cudaErrorInvalidValue;
+#undef RI_MP_BM
+#undef RI_MP
+    return ri_launch_status();
+}
+
+RI_API int ri_moe_combine(const float* Y, const int* place, const float* weights, const void* shared, int shared_dtype,
+                          void* out, int out_dtype, int T, int top, int d, int* counts, int E, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+#define RI_MC(TS, TO) RI_CHECKED(ri_launch(moe_combine_kernel<TS, TO>, dim3(T), dim3(256), 0, s, Y, place, weights, \
+        (const TS*)shared, (TO*)out, top, d, counts, E))
+    if (shared_dtype == RI_BF16 && out_dtype == RI_BF16) RI_MC(bf16, bf16);
+    else if (shared_dtype == RI_BF16) RI_MC(bf16, float);
+    else if (out_dtype == RI_BF16) RI_MC(float, bf16);
+    else RI_MC(float, float);
+#undef RI_MC
+    return ri_launch_status();
+}

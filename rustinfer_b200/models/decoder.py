@@ -9,7 +9,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts import attention, ffn, linear_attention, norm, parallel, rope, stem_tail  # noqa: F401  (registers the built-in parts)
+from ..parts import attention, experts, ffn, hyper, linear_attention, norm, parallel, rope, stem_tail  # noqa: F401  (registers the built-in parts)
 from ..parts.base import EMBEDDINGS, HEADS, NORMS, BuildContext, CacheNeed, ParamDecl, StepContext, StepIndex
 from ..parts.block import Block, Hidden
 from ..parts.spec import ModelSpec
@@ -24,6 +24,7 @@ class Decoder:
         self.embed = EMBEDDINGS.build(spec.embed_spec())
         self.head = HEADS.build(spec.head_spec())
         self.chained = None
+        self.layer_tap = None              # callable(run entry, Hidden) after every layer, for inspection
         for i, e in enumerate(spec.run_order):
             mixer = self.blocks[e.layer].mixer
             if e.cache_of is not None:
@@ -37,9 +38,13 @@ class Decoder:
         """Full tensor name -> declaration, for the loader and the random-weights mode."""
         s = self.spec
         decls: Dict[str, ParamDecl] = {}
+        # the stem first: where a prefix of the head's name is the stem's (a head called `head` beside
+        # nothing else), no declaration may hide another
         for prefix, part in ((s.embed_name, self.embed), (s.head_name, self.head),
                              (s.final_norm_name, self.final_norm)):
             for name, d in part.param_decls().items():
+                if prefix + name in decls:
+                    raise ValueError(f"two parts declare the tensor {prefix + name!r}")
                 decls[prefix + name] = d
         for block, ls in zip(self.blocks, s.layers):
             for role, part in block.roles().items():
@@ -99,12 +104,24 @@ class Decoder:
         s = self.spec
         if self.chained is not None and self.chained.takes(step):
             return self.chained.forward(step, caches, logit_rows)
-        h = torch.empty((step.num_tokens, s.hidden_size), dtype=torch.float32, device=self.ctx.device)
-        self.embed.forward(step, h)
-        hidden = Hidden(h, None)
+        if s.streams:
+            # several residual streams, all equal to the embedding's output at first: only the first is
+            # written until a sublayer's output has been mixed in
+            h = torch.empty((s.streams, step.num_tokens, s.hidden_size), dtype=torch.float32, device=self.ctx.device)
+            self.embed.forward(step, h[0])
+            hidden = Hidden(h, None, fresh=True)
+        else:
+            h = torch.empty((step.num_tokens, s.hidden_size), dtype=torch.float32, device=self.ctx.device)
+            self.embed.forward(step, h)
+            hidden = Hidden(h, None)
         for i, e in enumerate(s.run_order):
             self.blocks[e.layer].forward(hidden, step, caches[i])
+            if self.layer_tap is not None:
+                self.layer_tap(i, hidden)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
-        n = self.final_norm.add_norm(hidden.stream, hidden.pending, rows=logit_rows)
+        if s.streams:
+            n = hyper.finish(hidden, self.final_norm, logit_rows, self.ctx.dtype)
+        else:
+            n = self.final_norm.add_norm(hidden.stream, hidden.pending, rows=logit_rows)
         return self.head.forward(n)

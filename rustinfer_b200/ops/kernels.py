@@ -395,10 +395,11 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
                     cu_q: torch.Tensor, kv_len: torch.Tensor, tile_entry: torch.Tensor,
                     tile_q0: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: Optional[int], block: Optional[int] = None,
-                    value_dim: Optional[int] = None) -> None:
+                    value_dim: Optional[int] = None, sink: bool = False) -> None:
     """q [T, >=Hq*hd] (may be a column view of the qkv buffer), out [T, Hq*vd].  `block`: a query
     sees only the keys of its own block of that many positions (counted from 0).  `value_dim`:
-    size of a value where it is not the keys'; the cache is then [pages, Hkv*page*(hd+vd)]."""
+    size of a value where it is not the keys'; the cache is then [pages, Hkv*page*(hd+vd)].  `sink`:
+    the softmax's denominator has one added (a key of score 0 without a value)."""
     require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_q0)
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
                  (tile_entry, "tile_entry"), (tile_q0, "tile_q0")):
@@ -415,7 +416,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
                                  dtype_code(cache.dtype), _p(block_table), block_table.stride(0),
                                  _p(cu_q), _p(kv_len), _p(tile_entry), _p(tile_q0), tile_entry.numel(),
                                  num_heads, num_kv_heads, page_size, float(scale),
-                                 int(window) if window else 0, int(block) if block else 0, stream_ptr()),
+                                 int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
+                                 stream_ptr()),
           "attention_plain")
 
 
@@ -428,7 +430,7 @@ def attention_single_supports(num_heads: int, num_kv_heads: int, head_dim: int, 
 def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      cu_q: torch.Tensor, kv_len: torch.Tensor, entry_list: torch.Tensor, num_heads: int,
                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                     block: Optional[int] = None, value_dim: Optional[int] = None) -> None:
+                     block: Optional[int] = None, value_dim: Optional[int] = None, sink: bool = False) -> None:
     """Attention of the entries that bring one token (`entry_list`, int32; -1 skips): fp32 arithmetic, a kv
     head's keys and values read once for all its query heads.  Arguments as `attention_plain`."""
     require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list)
@@ -443,7 +445,8 @@ def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
     check(lib.ri_attention_single(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), dtype_code(cache.dtype),
                                   _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list),
                                   entry_list.numel(), num_heads, num_kv_heads, page_size, float(scale),
-                                  int(window) if window else 0, int(block) if block else 0, stream_ptr()),
+                                  int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
+                                  stream_ptr()),
           "attention_single")
 
 
@@ -538,6 +541,162 @@ def head_norm_scatter(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_wei
                                         dtype_code(ws[0].dtype) if ws else 0, 1 if value_norm else 0, float(eps),
                                         _p(slot_of_token), _p(cache), qkv.shape[0], num_heads, num_kv_heads,
                                         head_dim, value_dim, page, stream_ptr()), "head_norm_scatter")
+
+
+def embed_rmsnorm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[t,:] (fp32) = table[ids[t],:] / sqrt(mean(row^2) + eps) * weight."""
+    require_cuda(ids, table, weight, out)
+    _i32(ids, "ids"); _contig(table, "table"); _contig(weight, "weight")
+    d = table.shape[1]
+    if out.dtype != torch.float32 or out.shape != (ids.numel(), d) or not out.is_contiguous() or weight.numel() != d:
+        raise KernelError(f"embed_rmsnorm: out must be contiguous fp32 [{ids.numel()}, {d}], weight [{d}]")
+    check(L.core().ri_embed_rmsnorm(_p(ids), _p(table), dtype_code(table.dtype), _p(weight), dtype_code(weight.dtype),
+                                    float(eps), _p(out), ids.numel(), d, table.shape[0], stream_ptr()), "embed_rmsnorm")
+
+
+HYPER_MAX_STREAMS = 8
+
+
+def hyper_collect(streams: torch.Tensor, fresh: bool, y: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                  write: Optional[torch.Tensor], read: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+                  eps: float, out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> None:
+    """Several residual streams X [S, T, d] fp32 (`fresh`: only X[0] is written yet and stands for all).
+    With `y` [T, d]: X_t <- sum_s mix[s, t] X_s + write[t] y (stored unless `rows` is given).  Then
+    u = sum_s read[s] X_s (`read` None: the plain sum) and out = rmsnorm(u) * weight (`weight` None: out = u).
+    With `rows` (int32 [R]) only those tokens are read and out is [R, d]."""
+    require_cuda(streams, y, mix, write, read, weight, out, rows)
+    _contig(streams, "streams"); _i32(rows, "rows")
+    if streams.dtype != torch.float32 or streams.dim() != 3:
+        raise KernelError("hyper_collect: the streams are fp32 [S, T, d]")
+    S, T, d = streams.shape
+    if not 1 <= S <= HYPER_MAX_STREAMS:
+        raise KernelError(f"hyper_collect: 1 to {HYPER_MAX_STREAMS} streams")
+    if y is not None:
+        _contig(y, "y")
+        if y.shape != (T, d) or mix is None or write is None or tuple(mix.shape) != (S, S) or write.numel() != S \
+                or mix.dtype != torch.float32 or write.dtype != torch.float32 or not mix.is_contiguous():
+            raise KernelError("hyper_collect: y is [T, d], mix fp32 [S, S], write fp32 [S]")
+    if read is not None and (read.numel() != S or read.dtype != torch.float32):
+        raise KernelError("hyper_collect: read is fp32 [S]")
+    n_rows = T if rows is None else rows.numel()
+    if out is not None:
+        _contig(out, "out")
+        if out.shape != (n_rows, d):
+            raise KernelError(f"hyper_collect: out must be [{n_rows}, {d}]")
+    if weight is not None:
+        _contig(weight, "weight")
+        if weight.numel() != d:
+            raise KernelError("hyper_collect: weight has d elements")
+    check(L.core().ri_hyper_collect(_p(streams), 1 if fresh else 0, _p(y), dtype_code(y.dtype) if y is not None else 0,
+                                    _p(mix), _p(write), _p(read), _p(weight),
+                                    dtype_code(weight.dtype) if weight is not None else 0, float(eps), _p(out),
+                                    dtype_code(out.dtype) if out is not None else 0, _p(rows), n_rows, T, d, S,
+                                    stream_ptr()), "hyper_collect")
+
+
+def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
+                k_weight: Optional[torch.Tensor], norm_mode: int, eps: float, positions: torch.Tensor,
+                cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+                slot_of_token: Optional[torch.Tensor], cache: Optional[torch.Tensor], q_out: torch.Tensor,
+                num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, has_kv: bool) -> None:
+    """qkv [T, Hq*hd (+ Hkv*hd + Hkv*vd when `has_kv`)]: add `bias` (fp32), norm q and k (`norm_mode` 0: not;
+    1: every head by its own root mean square, weights [hd]; 2: all heads at once, weights [Hq*hd] and
+    [Hkv*hd]), rotate the first `rotary_dim` channels of every head (pairs (2i, 2i+1) when `interleaved`, else
+    (i, i + rotary_dim/2)), write q into q_out [T, Hq*hd] and k, v into the cache at slot_of_token[t]."""
+    require_cuda(qkv, bias, q_weight, k_weight, positions, cos, sin, slot_of_token, cache, q_out)
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token")
+    T = qkv.shape[0]
+    cols = num_heads * head_dim + (num_kv_heads * (head_dim + value_dim) if has_kv else 0)
+    if qkv.stride(1) != 1 or qkv.shape[1] != cols:
+        raise KernelError(f"qkv_prepare: qkv must be [T, {cols}] with unit column stride")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != cols or not bias.is_contiguous()):
+        raise KernelError(f"qkv_prepare: bias is fp32 [{cols}]")
+    _contig(q_out, "q_out")
+    if q_out.shape != (T, num_heads * head_dim):
+        raise KernelError("qkv_prepare: q_out is [T, Hq*hd]")
+    ws = [w for w in (q_weight, k_weight) if w is not None]
+    want = {0: (0, 0), 1: (head_dim, head_dim), 2: (num_heads * head_dim, num_kv_heads * head_dim)}[norm_mode]
+    for w, n in zip((q_weight, k_weight), want):
+        if w is not None and (w.numel() != n or w.dtype != ws[0].dtype or not w.is_contiguous()):
+            raise KernelError("qkv_prepare: the norm weights' sizes do not fit the norm mode")
+    if norm_mode and (q_weight is None or (has_kv and k_weight is None)):
+        raise KernelError("qkv_prepare: a norm needs its weights")
+    if rotary_dim and (cos is None or sin is None or cos.dtype != torch.float32 or sin.dtype != torch.float32
+                       or cos.shape[1] != rotary_dim // 2 or not cos.is_contiguous() or not sin.is_contiguous()):
+        raise KernelError("qkv_prepare: cos/sin are fp32 [positions, rotary_dim/2]")
+    page = 1
+    if cache is not None:
+        _contig(cache, "cache")
+        if cache.dtype != q_out.dtype:
+            raise KernelError("qkv_prepare: the cache has q_out's dtype")
+        page = paged_cache_page_size(cache, num_kv_heads, head_dim, value_dim)
+    check(L.core().ri_qkv_prepare(_p(qkv), dtype_code(qkv.dtype), qkv.stride(0), _p(bias), _p(q_weight), _p(k_weight),
+                                  dtype_code(ws[0].dtype) if ws else 0, int(norm_mode), float(eps), _p(positions),
+                                  _p(cos), _p(sin), int(rotary_dim), 1 if interleaved else 0, _p(slot_of_token), _p(cache),
+                                  _p(q_out), dtype_code(q_out.dtype), T, num_heads, num_kv_heads, head_dim, value_dim,
+                                  1 if has_kv else 0, page, stream_ptr()), "qkv_prepare")
+
+
+# ------------------------------------------------------------------------ routed experts
+def moe_route(z: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int, keep: int, renorm: bool,
+              ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor) -> None:
+    """Router logits z [T, E] fp32 -> the `top` experts of every token (ids int32 [T, top]) and their weights
+    (fp32 [T, top]): scores sigmoid(z), chosen by score + correction among the experts of the `keep` best of
+    `n_groups` groups (0: no groups).  counts (int32 [E]) gets one added per choice."""
+    require_cuda(z, correction, ids, weights, counts)
+    T, E = z.shape
+    _contig(z, "z"); _contig(ids, "ids"); _contig(weights, "weights"); _i32(ids, "ids"); _i32(counts, "counts")
+    if z.dtype != torch.float32 or weights.dtype != torch.float32 or ids.shape != (T, top) or weights.shape != (T, top) \
+            or counts.numel() != E or (correction is not None and (correction.dtype != torch.float32 or correction.numel() != E)):
+        raise KernelError("moe_route: z fp32 [T, E], correction fp32 [E], ids int32 and weights fp32 [T, top], counts [E]")
+    check(L.core().ri_moe_route(_p(z), _p(correction), T, E, int(top), int(n_groups), int(keep), 1 if renorm else 0,
+                                _p(ids), _p(weights), _p(counts), stream_ptr()), "moe_route")
+
+
+def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """The (token, choice) pairs in expert order: offsets int32 [E + 1], order int32 [N] (pair at each place),
+    place int32 [N] (place of each pair); pairs of one expert keep their order."""
+    require_cuda(ids, counts, offsets, order, place)
+    N, E = ids.numel(), counts.numel()
+    for t, n in ((ids, "ids"), (counts, "counts"), (offsets, "offsets"), (order, "order"), (place, "place")):
+        _i32(t, n); _contig(t, n)
+    if offsets.numel() != E + 1 or order.numel() != N or place.numel() != N:
+        raise KernelError("moe_sort: offsets [E + 1], order and place [N]")
+    check(L.core().ri_moe_sort(_p(ids), _p(counts), N, E, _p(offsets), _p(order), _p(place), stream_ptr()), "moe_sort")
+
+
+def moe_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: Optional[torch.Tensor],
+                top: int, gated: bool) -> None:
+    """Rows in expert order times their expert's matrix w [E, Ntot, K]: row p is a[order[p] // top] when `order`
+    is given, else a[p].  gated: Ntot = 2N, out[p] = silu(a w_e[:N]^T) * (a w_e[N:]^T); else out[p] = a w_e^T.
+    fp32 sums in the order of k."""
+    require_cuda(a, w, out, offsets, order)
+    _contig(w, "w"); _i32(offsets, "offsets"); _i32(order, "order")
+    E, Ntot, Kd = w.shape
+    N = Ntot // 2 if gated else Ntot
+    rows = out.shape[0]
+    if a.stride(1) != 1 or a.shape[1] != Kd or out.stride(1) != 1 or out.shape[1] != N or offsets.numel() != E + 1 \
+            or (order is not None and order.numel() != rows) or (order is None and a.shape[0] != rows):
+        raise KernelError(f"moe_product: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    check(L.core().ri_moe_product(_p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype), _p(out),
+                                  dtype_code(out.dtype), out.stride(0), _p(offsets), _p(order), int(top),
+                                  1 if order is not None else 0, rows, E, N, Kd, 1 if gated else 0, stream_ptr()),
+          "moe_product")
+
+
+def moe_combine(Y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
+                out: torch.Tensor, counts: torch.Tensor) -> None:
+    """out[t] = sum_j weights[t, j] * Y[place[t * top + j]] (+ shared[t]); counts is put back to zero."""
+    require_cuda(Y, place, weights, shared, out, counts)
+    T, top = weights.shape
+    d = Y.shape[1]
+    _contig(Y, "Y"); _contig(out, "out"); _contig(weights, "weights"); _i32(place, "place"); _i32(counts, "counts")
+    if Y.dtype != torch.float32 or weights.dtype != torch.float32 or Y.shape[0] != T * top or out.shape != (T, d) \
+            or place.numel() != T * top or (shared is not None and (shared.shape != (T, d) or not shared.is_contiguous())):
+        raise KernelError("moe_combine: Y fp32 [T*top, d], weights fp32 [T, top], shared and out [T, d]")
+    check(L.core().ri_moe_combine(_p(Y), _p(place), _p(weights), _p(shared),
+                                  dtype_code(shared.dtype) if shared is not None else 0, _p(out), dtype_code(out.dtype),
+                                  T, top, d, _p(counts), counts.numel(), stream_ptr()), "moe_combine")
 
 
 GATE_SILU, GATE_SIGMOID = 0, 1
@@ -691,7 +850,8 @@ def mma_tokens_per_tile(num_heads: int, num_kv_heads: int) -> int:
 
 def attention_prefill_bf16(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0,
                            num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                           window: Optional[int], block: Optional[int] = None, precise: bool = False) -> None:
+                           window: Optional[int], block: Optional[int] = None, precise: bool = False,
+                           sink: bool = False) -> None:
     """Tiles are (entry, first token) pairs of `mma_tokens_per_tile` tokens each.  `block`: a query
     sees only the keys of its own block of that many positions.  `precise`: the softmax weights go
     into the product with the values in full fp32 (as three bf16 pieces) instead of rounded to bf16."""
@@ -703,7 +863,7 @@ def attention_prefill_bf16(q, out, cache, block_table, cu_q, kv_len, tile_entry,
                                         block_table.stride(0), _p(cu_q), _p(kv_len), _p(tile_entry),
                                         _p(tile_tok0), tile_entry.numel(), num_heads, num_kv_heads,
                                         cache.shape[3], float(scale), int(window) if window else 0,
-                                        int(block) if block else 0, 1 if precise else 0,
+                                        int(block) if block else 0, 1 if precise else 0, 1 if sink else 0,
                                         stream_ptr()), "attention_prefill_bf16")
 
 

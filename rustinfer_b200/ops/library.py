@@ -29,7 +29,7 @@ _SIGNATURES = {
     "ri_decode_feedback": [_P, _P, _I, _P, _P, _I, _P, _P, _P],
     "ri_sample": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "ri_sample_by_sorting": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
-    "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _L, _P, _I, _P],
     "ri_attention_mma_tokens_per_tile": [_I],
     "ri_attention_prefill_tc": [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -38,8 +38,15 @@ _SIGNATURES = {
     "ri_gemm_tc_rope": [_P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "ri_decode_chain": [_P, _I, _P, _I, _P, _P, _I, _P],
     "ri_decode_chain_fits": [_P, _I, _I, _I],
-    "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
-    "ri_attention_single": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ri_attention_single": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ri_embed_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
+    "ri_hyper_collect": [_P, _I, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _I, _P],
+    "ri_qkv_prepare": [_P, _I, _I, _P, _P, _P, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ri_moe_route": [_P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "ri_moe_sort": [_P, _P, _I, _I, _P, _P, _P, _P],
+    "ri_moe_product": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ri_moe_combine": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P],
     "ri_attention_single_supports": [_I, _I],
     "ri_embed_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     "ri_sandwich_norm": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _F, _P],
@@ -53,7 +60,8 @@ _SIGNATURES = {
     "ri_delta_prepare": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _F, _F, _P, _P, _I, _I, _I, _P],
 }
 
-_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "sampling.cu", "sequence_parts.cu"]
+_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "sampling.cu", "sequence_parts.cu", "stream_parts.cu",
+                 "mixture_parts.cu"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 
 

@@ -31,9 +31,15 @@ class GQAAttention(Mixer):
     are divided by their root mean square over head_dim and multiplied by the weights
     `q_norm` / `k_norm` [head_dim], shared by the heads), `value_norm_eps` (v of every head is divided
     by its root mean square; it is cached so), `tensor_names` (local name -> name in the file, for
-    checkpoints that call q_proj.weight and the others something else).  A mixer with any of the
-    first four runs on the fp32-arithmetic attention kernel in both precisions: scores, softmax
-    weights and the weighted sum of values are 32-bit there."""
+    checkpoints that call q_proj.weight and the others something else), `bias` (q, k and v have biases
+    `q_proj.bias` and so on, added in the projection), `qk_norm` ("head", the default; "whole": one RMS norm
+    over all heads of q, and one over all of k, with weights of that size, before the rotation), `sink` (the
+    softmax's denominator has one added: a key of score 0 that has no value), `cache_window` (keys the cache
+    keeps where that is more than `window`: other layers with wider windows read this layer's cache),
+    `output` ("float32": the sublayer's output leaves the output projection in 32-bit).  A mixer with any
+    of these but the last two runs on the fp32-arithmetic attention kernels in both precisions: scores,
+    softmax weights and the weighted sum of values are 32-bit there.  With `position`, the rotary part's
+    `layout` says which channels pair up."""
 
     graph_safe = True
     adds_to_residual = True
@@ -52,9 +58,26 @@ class GQAAttention(Mixer):
         self.qk_norm_eps = float(p["qk_norm_eps"]) if p.get("qk_norm_eps") is not None else None
         self.value_norm_eps = float(p["value_norm_eps"]) if p.get("value_norm_eps") is not None else None
         self.tensor_names = dict(p.get("tensor_names") or {})
-        # options only the plain kernel and the head-norm kernel serve
+        self.bias = bool(p.get("bias", False))
+        self.qk_norm = str(p.get("qk_norm", "head"))
+        if self.qk_norm not in ("head", "whole"):
+            raise ValueError(f"qk_norm {self.qk_norm!r}: known are 'head' and 'whole'")
+        self.sink = bool(p.get("sink", False))
+        self.cache_window = (int(p["cache_window"]) if p.get("cache_window") else None) if "cache_window" in p else self.window
+        if self.window is None and self.cache_window is not None:
+            raise ValueError("a mixer that sees every key cannot read a cache that keeps a window")
+        if self.window and self.cache_window and self.cache_window < self.window:
+            raise ValueError(f"the cache keeps {self.cache_window} keys, the mask wants {self.window}")
+        self.out_fp32 = str(p.get("output", "")) == "float32"
+        whole = self.qk_norm_eps is not None and self.qk_norm == "whole"
+        # options only the plain kernels serve
         self.general = (self.vd != self.hd or self.block is not None or self.qk_norm_eps is not None
-                        or self.value_norm_eps is not None)
+                        or self.value_norm_eps is not None or self.bias or self.sink)
+        # q, k, v leave the projection in 32-bit and one kernel adds biases, norms, rotates and writes the cache
+        self.prepared = self.general and (self.bias or whole or self.sink or p.get("position") is not None
+                                          or not self.own_kv)
+        if self.prepared and self.value_norm_eps is not None:
+            raise ValueError("values of unit root mean square are built for mixers without biases, rotation or a sink")
         if self.Hq % self.Hkv:
             raise ValueError(f"{self.Hq} heads are not a multiple of {self.Hkv} kv heads")
         if self.general:
@@ -81,13 +104,19 @@ class GQAAttention(Mixer):
             d[self._name("k_proj.weight")] = ParamDecl((kv, self.hidden))
             d[self._name("v_proj.weight")] = ParamDecl((self.Hkv * self.vd, self.hidden))
         if self.qk_norm_eps is not None:
-            d[self._name("q_norm")] = ParamDecl((self.hd,), init="ones")
+            whole = self.qk_norm == "whole"
+            d[self._name("q_norm")] = ParamDecl((q if whole else self.hd,), init="ones")
             if self.own_kv:
-                d[self._name("k_norm")] = ParamDecl((self.hd,), init="ones")
+                d[self._name("k_norm")] = ParamDecl((kv if whole else self.hd,), init="ones")
+        if self.bias:
+            d[self._name("q_proj.bias")] = ParamDecl((q,), init="zeros")
+            if self.own_kv:
+                d[self._name("k_proj.bias")] = ParamDecl((kv,), init="zeros")
+                d[self._name("v_proj.bias")] = ParamDecl((self.Hkv * self.vd,), init="zeros")
         return d
 
     def cache_need(self):
-        return PagedKV(self.Hkv, self.hd, self.window, value_dim=self.vd if self.vd != self.hd else None,
+        return PagedKV(self.Hkv, self.hd, self.cache_window, value_dim=self.vd if self.vd != self.hd else None,
                        block=self.block)
 
     def prepare(self, ctx: BuildContext) -> None:
@@ -162,11 +191,30 @@ class GQAAttention(Mixer):
             self.q_norm = tensors[self._name("q_norm")].contiguous()
             if self.own_kv:
                 self.k_norm = tensors[self._name("k_norm")].to(self.q_norm.dtype).contiguous()
+        self.qkv_bias = None
+        if self.bias:
+            names = ["q_proj.bias"] + (["k_proj.bias", "v_proj.bias"] if self.own_kv else [])
+            self.qkv_bias = torch.cat([tensors[self._name(n)].to(torch.float32) for n in names]).contiguous()
 
     def _project_out(self, out: torch.Tensor, residual: Optional[torch.Tensor]):
         if residual is not None and self.o.add_into(out, residual):
             return None
-        return self.o(out, out_dtype=self.ctx.dtype)
+        return self.o(out, out_dtype=torch.float32 if self.out_fp32 else self.ctx.dtype)
+
+    def _prepared_forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache, writes: bool):
+        """q, k, v in 32-bit out of the projection; one kernel adds the biases, norms q and k, rotates them,
+        rounds q to the activation dtype and writes k and v into their pages."""
+        g = step.groups[cache.group]
+        qkv = self.qkv(x, out_dtype=torch.float32)
+        q = torch.empty((x.shape[0], self.Hq * self.hd), dtype=self.ctx.dtype, device=x.device)
+        pos = self.position
+        K.qkv_prepare(qkv, self.qkv_bias, self.q_norm, self.k_norm,
+                      0 if self.qk_norm_eps is None else 2 if self.qk_norm == "whole" else 1,
+                      self.qk_norm_eps or 0.0, step.positions, pos.cos if pos else None, pos.sin if pos else None,
+                      pos.rotary_dim if pos else 0, bool(pos and pos.layout == "interleaved"),
+                      g.slot_of_token if writes else None, cache.kv if writes else None, q,
+                      self.Hq, self.Hkv, self.hd, self.vd, self.own_kv)
+        return q
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache,
                 residual: Optional[torch.Tensor] = None):
@@ -182,6 +230,9 @@ class GQAAttention(Mixer):
                               g.slot_of_token if writes else None, cache.kv if writes else None,
                               self.Hq, self.Hkv if writes else 0, self.hd):
                 return self._project_out(self.attend(q, step, cache), residual)
+        if self.prepared:
+            q = self._prepared_forward(x, step, cache, writes)
+            return self._project_out(self.attend(q, step, cache), residual)
         qkv = self.qkv(x, out_dtype=self.ctx.dtype)
         if self.general:
             if self.position is not None or not self.own_kv:
@@ -228,24 +279,25 @@ class GQAAttention(Mixer):
             (single,) = step.index(self._single)
             if single.numel() and self.fast_single:
                 K.attention_single(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single, self.Hq, self.Hkv,
-                                   self.hd, self.scale, self.window, self.block, self.vd)
+                                   self.hd, self.scale, self.window, self.block, self.vd, sink=self.sink)
             elif single.numel():                      # every single token is a tile of one row
                 K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single,
                                   self._zeros[: single.numel()], self.Hq, self.Hkv, self.hd, self.scale,
-                                  self.window, self.block, self.vd)
+                                  self.window, self.block, self.vd, sink=self.sink)
             tile_entry, tile_tok0 = step.index(self._tiles)
             if tile_entry.numel() and self.precise_mma:
                 K.attention_prefill_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry,
                                          tile_tok0, self.Hq, self.Hkv, self.hd, self.scale, self.window,
-                                         self.block, precise=True)
+                                         self.block, precise=True, sink=self.sink)
             elif tile_entry.numel():
                 K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
-                                  self.Hq, self.Hkv, self.hd, self.scale, self.window, self.block, self.vd)
+                                  self.Hq, self.Hkv, self.hd, self.scale, self.window, self.block, self.vd,
+                                  sink=self.sink)
             return out
         if not self.use_mma:
             tile_entry, tile_q0 = step.index(self._tiles)
             K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
-                              self.Hq, self.Hkv, self.hd, self.scale, self.window, self.block, self.vd)
+                              self.Hq, self.Hkv, self.hd, self.scale, self.window, self.block, self.vd, sink=self.sink)
             return out
         (single,) = step.index(self._single)
         if single.numel():

@@ -20,8 +20,9 @@ from .spec import LayerSpec
 
 @dataclass
 class Hidden:
-    stream: torch.Tensor                # [T, hidden] fp32
+    stream: torch.Tensor                # [T, hidden] fp32 ([streams, T, hidden] in a model of several streams)
     pending: Optional[torch.Tensor]     # [T, hidden] activation dtype, not yet added
+    fresh: bool = False                 # several streams of which only the first is written yet (all are equal)
 
 
 class Block:
@@ -99,7 +100,21 @@ def _sandwich(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
     hidden.pending = NormedDelta(block.ffn.forward(x, step), post_ffn)
 
 
-ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm, "sandwich": _sandwich}
+def _hyper(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
+    """Several residual streams (see parts/hyper.py): each sublayer reads a weighted sum of the streams
+    through its `hyper_rmsnorm`, and its output stays pending until the next read of the streams mixes
+    them and adds it to each with a weight of its own.  The feed-forward is optional."""
+    from .hyper import HyperPending, HyperRMSNorm
+    if not isinstance(block.mixer_norm, HyperRMSNorm) or (block.ffn is not None and not isinstance(block.ffn_norm, HyperRMSNorm)):
+        raise ValueError("the hyper arrangement wants a hyper_rmsnorm before each sublayer")
+    x = block.mixer_norm.collect(hidden)
+    hidden.pending = HyperPending(block.mixer.forward(x, step, cache), block.mixer_norm)
+    if block.ffn is not None:
+        x = block.ffn_norm.collect(hidden)
+        hidden.pending = HyperPending(block.ffn.forward(x, step), block.ffn_norm)
+
+
+ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm, "sandwich": _sandwich, "hyper": _hyper}
 
 
 def register_arrangement(name: str, fn: Callable) -> None:

@@ -1,0 +1,126 @@
+"""A feed-forward of routed experts: every token runs through `top` of `experts` small gated feed-forwards,
+chosen by a router, and through a shared one where the model has it.
+
+    z = W_r x (32-bit);  s = sigmoid(z);  choice score c = s + correction
+    with groups: the experts form `groups_count` equal groups of neighbours; a group's score is the sum of
+        its two largest c; only experts of the `groups_keep` best groups can be chosen
+    the `top` largest c are chosen; their weights are the s (divided by their sum when `renormalize`)
+    y = sum_chosen weight_e * down_e( silu(gate_e x) * up_e x ) + shared(x)
+
+The router's product, scores and choice are fp32.  The (token, choice) pairs are sorted by expert on the
+device and the experts' products run over the sorted rows; no count visits the host, so the part can be
+captured in a step's CUDA graph.  The reference engine has dense feed-forwards only
+(crates/infer-worker/src/components/ffn_dense.rs:26-33); its loader names expert tensors but runs none.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..ops import kernels as K
+from .base import FEED_FORWARDS, FeedForward, ParamDecl, StepContext, register_feed_forward
+from .linear import Linear
+from .spec import PartSpec
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """params: hidden_size, expert_ff, experts, top, groups_count / groups_keep (None: no groups), shared_ff
+    (None: no shared expert), score ("sigmoid"), correction (the router has a tensor added to the scores for
+    the choice), renormalize, output ("float32", the default, or the activation dtype); tensor names:
+    expert_prefix (default "e{}."; `{}` is the expert's number), gate_name / up_name / down_name (default
+    "gate" / "up" / "down"), router_name ("router"), correction_name ("correction"), shared_prefix ("shared.")."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        p = params
+        self.hidden, self.ff = int(p["hidden_size"]), int(p["expert_ff"])
+        self.E, self.top = int(p["experts"]), int(p["top"])
+        self.groups = int(p["groups_count"]) if p.get("groups_count") else 0
+        self.keep = int(p["groups_keep"]) if p.get("groups_keep") else 0
+        self.shared_ff = int(p["shared_ff"]) if p.get("shared_ff") else None
+        if str(p.get("score", "sigmoid")) != "sigmoid":
+            raise ValueError("the router's scores are sigmoids; no other kind is built")
+        self.has_correction = bool(p.get("correction", False))
+        self.renorm = bool(p.get("renormalize", False))
+        self.out_fp32 = str(p.get("output", "float32")) == "float32"
+        self.expert_prefix = str(p.get("expert_prefix", "e{}."))
+        self.names = {k: str(p.get(k + "_name", k)) for k in ("gate", "up", "down", "router", "correction")}
+        self.shared_prefix = str(p.get("shared_prefix", "shared."))
+        if not 1 <= self.top <= min(self.E, 32):
+            raise ValueError(f"a token uses 1 to min(experts, 32) experts, got {self.top} of {self.E}")
+        if self.groups and (self.E % self.groups or not 0 < self.keep <= self.groups
+                            or self.keep * (self.E // self.groups) < self.top):
+            raise ValueError("groups_count divides experts, and the groups kept hold at least `top` experts")
+        self.shared: Optional[FeedForward] = None
+        if self.shared_ff:
+            self.shared = FEED_FORWARDS.build(PartSpec("swiglu", {"hidden_size": self.hidden,
+                                                                  "intermediate_size": self.shared_ff,
+                                                                  "output": "float32"}))
+        self._shared_names = {"gate_proj.weight": self.names["gate"], "up_proj.weight": self.names["up"],
+                              "down_proj.weight": self.names["down"]}
+
+    @property
+    def graph_safe(self) -> bool:
+        return True
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        d: Dict[str, ParamDecl] = {}
+        for e in range(self.E):
+            pre = self.expert_prefix.format(e)
+            d[pre + self.names["gate"]] = ParamDecl((self.ff, self.hidden))
+            d[pre + self.names["up"]] = ParamDecl((self.ff, self.hidden))
+            d[pre + self.names["down"]] = ParamDecl((self.hidden, self.ff))
+        d[self.names["router"]] = ParamDecl((self.E, self.hidden))
+        if self.has_correction:
+            d[self.names["correction"]] = ParamDecl((self.E,), init="zeros")
+        if self.shared is not None:
+            for local, decl in self.shared.param_decls().items():
+                d[self.shared_prefix + self._shared_names[local]] = decl
+        return d
+
+    def prepare(self, ctx) -> None:
+        super().prepare(ctx)
+        if self.shared is not None:
+            self.shared.prepare(ctx)
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        pre = [self.expert_prefix.format(e) for e in range(self.E)]
+        # per expert the gate rows, then the up rows: [E, 2 ff, hidden]; the down matrices [E, hidden, ff]
+        self.gate_up = torch.stack([torch.cat([tensors[p + n["gate"]], tensors[p + n["up"]]], dim=0) for p in pre]).contiguous()
+        self.down = torch.stack([tensors[p + n["down"]] for p in pre]).contiguous()
+        # the router is 32-bit in both engines: its product goes through the exact fp32 kernel
+        self.router = Linear(tensors[n["router"]].to(torch.float32), self.ctx.num_sms)
+        self.correction = tensors[n["correction"]].to(torch.float32).contiguous() if self.has_correction else None
+        self.counts = torch.zeros(self.E, dtype=torch.int32, device=self.gate_up.device)   # the kernels leave it zero
+        if self.shared is not None:
+            self.shared.load({local: tensors[self.shared_prefix + name] for local, name in self._shared_names.items()})
+
+    def route(self, x: torch.Tensor):
+        """(ids int32 [T, top], weights fp32 [T, top]); adds the choices to `self.counts`."""
+        T = x.shape[0]
+        z = self.router(x, out_dtype=torch.float32)
+        ids = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
+        weights = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
+        K.moe_route(z, self.correction, self.top, self.groups, self.keep, self.renorm, ids, weights, self.counts)
+        return ids, weights
+
+    def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None):
+        T, dev = x.shape[0], x.device
+        N = T * self.top
+        ids, weights = self.route(x)
+        offsets = torch.empty(self.E + 1, dtype=torch.int32, device=dev)
+        order = torch.empty(N, dtype=torch.int32, device=dev)
+        place = torch.empty(N, dtype=torch.int32, device=dev)
+        K.moe_sort(ids, self.counts, offsets, order, place)
+        mid = torch.empty((N, self.ff), dtype=self.gate_up.dtype, device=dev)
+        K.moe_product(x if x.dtype == self.gate_up.dtype else x.to(self.gate_up.dtype), self.gate_up, mid, offsets,
+                      order, self.top, gated=True)
+        Y = torch.empty((N, self.hidden), dtype=torch.float32, device=dev)
+        K.moe_product(mid, self.down, Y, offsets, None, self.top, gated=False)
+        shared = self.shared.forward(x, step) if self.shared is not None else None
+        out = torch.empty((T, self.hidden), dtype=torch.float32 if self.out_fp32 else self.ctx.dtype, device=dev)
+        K.moe_combine(Y, place, weights, shared, out, self.counts)
+        return out

@@ -14,12 +14,14 @@ from .linear import Linear
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size."""
+    """params: hidden_size, intermediate_size, output ("float32": the result leaves the down projection in
+    32-bit, default the activation dtype)."""
 
     def __init__(self, params):
         super().__init__(params)
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
+        self.out_fp32 = str(params.get("output", "")) == "float32"
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
@@ -54,7 +56,7 @@ class SwiGLU(FeedForward):
             K.silu_mul(gu, m)
         if residual is not None and self.down.add_into(m, residual):
             return None
-        return self.down(m, out_dtype=self.ctx.dtype)
+        return self.down(m, out_dtype=torch.float32 if self.out_fp32 else self.ctx.dtype)
 
 
 _ACTIVATIONS = {"gelu": K.ACT_GELU_ERF, "gelu_erf": K.ACT_GELU_ERF, "tanh": K.ACT_TANH, "gelu_tanh": K.ACT_GELU_TANH}
@@ -64,7 +66,8 @@ _ACTIVATIONS = {"gelu": K.ACT_GELU_ERF, "gelu_erf": K.ACT_GELU_ERF, "tanh": K.AC
 class DenseMLP(FeedForward):
     """down( act(up(x)) ) without a gate.  params: hidden_size, intermediate_size, activation
     ("gelu": with erf; "gelu_tanh"; "tanh"), up_name / down_name (tensor names, default
-    "up_proj.weight" / "down_proj.weight").  The activation is computed in fp32."""
+    "up_proj.weight" / "down_proj.weight"), output ("float32": the result leaves the down projection in
+    32-bit).  The activation is computed in fp32."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -76,6 +79,7 @@ class DenseMLP(FeedForward):
         self.act = _ACTIVATIONS[act]
         self.up_name = str(params.get("up_name", "up_proj.weight"))
         self.down_name = str(params.get("down_name", "down_proj.weight"))
+        self.out_fp32 = str(params.get("output", "")) == "float32"
         self.up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
@@ -92,4 +96,4 @@ class DenseMLP(FeedForward):
         K.activation(u, u, self.act)
         if residual is not None and self.down.add_into(u, residual):
             return None
-        return self.down(u, out_dtype=self.ctx.dtype)
+        return self.down(u, out_dtype=torch.float32 if self.out_fp32 else self.ctx.dtype)

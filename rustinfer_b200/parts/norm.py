@@ -15,19 +15,20 @@ from .base import Norm, ParamDecl, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps."""
+    """params: size, eps, weight_name (the tensor's local name, default "weight")."""
 
     def __init__(self, params):
         super().__init__(params)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.weight_name = str(params.get("weight_name", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def param_decls(self) -> Dict[str, ParamDecl]:
-        return {"weight": ParamDecl((self.size,), init="ones")}
+        return {self.weight_name: ParamDecl((self.size,), init="ones")}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.weight_name].contiguous()
 
     def add_norm(self, h, delta, rows=None):
         n = h.shape[0] if rows is None else rows.numel()

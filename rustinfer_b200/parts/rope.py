@@ -44,7 +44,8 @@ def rope_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict]) -> Lis
 
 @register_position("rope")
 class RotaryEncoding(PositionEncoding):
-    """params: head_dim, rotary_dim, theta, scaling (dict or None)."""
+    """params: head_dim, rotary_dim, theta, scaling (dict or None), layout ("half": channel i turns with
+    channel i + rotary_dim/2, the default; "interleaved": channel 2i with channel 2i+1)."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -52,6 +53,9 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = int(params.get("rotary_dim") or self.head_dim)
         self.theta = float(params["theta"])
         self.scaling = dict(params["scaling"]) if params.get("scaling") else None
+        self.layout = str(params.get("layout", "half"))
+        if self.layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary layout {self.layout!r}: known are 'half' and 'interleaved'")
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.cos: Optional[torch.Tensor] = None

@@ -76,6 +76,9 @@ class ModelSpec:
     # linear head of the model's sizes
     embed: Optional[PartSpec] = None
     head: Optional[PartSpec] = None
+    # 0: one residual stream [tokens, hidden]; n >= 1: n streams [n, tokens, hidden] that the `hyper`
+    # block arrangement reads through weighted sums and the last norm adds up
+    streams: int = 0
 
     def embed_spec(self) -> PartSpec:
         return self.embed or PartSpec("token_embedding", {"vocab_size": self.vocab_size,

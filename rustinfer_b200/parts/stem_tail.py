@@ -71,23 +71,49 @@ class SinusoidEmbedding(TokenEmbedding):
                          self.freq, h)
 
 
+@register_embedding("normed_embedding")
+class NormedEmbedding(TokenEmbedding):
+    """h[t, :] = rmsnorm(E[ids[t], :]) * w: the looked-up row divided by its root mean square (eps inside the
+    root) and multiplied by a weight, in fp32.  params: vocab_size, hidden_size, eps, weight_name (the
+    table's local name, default "weight"), norm_name (the norm weight's, default "norm.weight")."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.eps = float(params["eps"])
+        self.weight_name = str(params.get("weight_name", "weight"))
+        self.norm_name = str(params.get("norm_name", "norm.weight"))
+        self.norm_weight: Optional[torch.Tensor] = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {self.weight_name: ParamDecl((self.vocab, self.hidden)),
+                self.norm_name: ParamDecl((self.hidden,), init="ones")}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.table = tensors[self.weight_name].contiguous()
+        self.norm_weight = tensors[self.norm_name].contiguous()
+
+    def forward(self, step: StepContext, h: torch.Tensor) -> None:
+        K.embed_rmsnorm(step.token_ids[: step.num_tokens], self.table, self.norm_weight, self.eps, h)
+
+
 @register_head("linear_head")
 class LinearHead(Head):
     """params: vocab_size, hidden_size, tied (the configuration says the head is the embedding
-    table: the file need not have a weight for it)."""
+    table: the file need not have a weight for it), weight_name (the tensor's local name, default "weight")."""
 
     def __init__(self, params):
         super().__init__(params)
         self.vocab, self.hidden = int(params["vocab_size"]), int(params["hidden_size"])
         self.tied = bool(params.get("tied", False))
+        self.weight_name = str(params.get("weight_name", "weight"))
         self.linear: Optional[Linear] = None
         self.is_tied = False
 
     def param_decls(self) -> Dict[str, ParamDecl]:
-        return {"weight": ParamDecl((self.vocab, self.hidden), optional=self.tied)}
+        return {self.weight_name: ParamDecl((self.vocab, self.hidden), optional=self.tied)}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        w = tensors.get("weight")
+        w = tensors.get(self.weight_name)
         self.is_tied = w is None
         if w is None:
             shared = self.shared
