@@ -61,28 +61,38 @@ def keys_and_values(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, 
     return k, v.view(-1, G, dv)
 
 
-def attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, eps: float, positions: torch.Tensor,
-              kv: Tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
-    """h [T, width] -> [T, width]; kv: the keys and values it reads (its own or an earlier layer's)."""
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    T = h.shape[0]
-    q = rms_norm(h @ w["q"].T + w["q.b"], w["q.norm"], eps).view(T, H, d)
-    rot = m.get("rot") or {}
-    q = rotate_pairs(q, positions, int(rot.get("dims", 0)), float(rot.get("base", 1.0)))
-    k, v = kv
-    window = (m.get("mask") or {}).get("size")
-    i = positions[:, None]
-    j = positions[None, :]
+def sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: Optional[int],
+                   sink: bool = True) -> torch.Tensor:
+    """q [T, H, d], k [T, G, d], v [T, G, dv] of positions 0..T-1 -> [T, H, dv].  Query i sees keys j with
+    0 <= i - j < window (every j <= i without a window); weights exp(s_j) / (1 + sum exp(s_j)): the one in
+    the denominator is a key of score 0 that has no value (left out when `sink` is False)."""
+    T, H, _ = q.shape
+    G, dv = k.shape[1], v.shape[2]
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
     seen = (j <= i)
     if window:
         seen = seen & (i - j < window)
     out = torch.zeros(T, H, dv, dtype=F64)
     for head in range(H):
         g = head // (H // G)
-        s = (q[:, head, :] @ k[:, g, :].T) * m["scale"]
+        s = (q[:, head, :].to(F64) @ k[:, g, :].to(F64).T) * scale
+        s = s - (0.0 if sink else s.masked_fill(~seen, -math.inf).max(dim=-1, keepdim=True).values)
         e = torch.where(seen, torch.exp(s), torch.zeros_like(s))
-        p = e / (1.0 + e.sum(dim=-1, keepdim=True))
-        out[:, head, :] = p @ v[:, g, :]
+        p = e / ((1.0 if sink else 0.0) + e.sum(dim=-1, keepdim=True))
+        out[:, head, :] = p @ v[:, g, :].to(F64)
+    return out
+
+
+def attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, eps: float, positions: torch.Tensor,
+              kv: Tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
+    """h [T, width] -> [T, width]; kv: the keys and values it reads (its own or an earlier layer's)."""
+    H, d, dv = m["heads"], m["dim"], m["vdim"]
+    T = h.shape[0]
+    q = rms_norm(h @ w["q"].T + w["q.b"], w["q.norm"], eps).view(T, H, d)
+    rot = m.get("rot") or {}
+    q = rotate_pairs(q, positions, int(rot.get("dims", 0)), float(rot.get("base", 1.0)))
+    out = sink_attention(q, kv[0], kv[1], m["scale"], (m.get("mask") or {}).get("size"))
     return out.reshape(T, H * dv) @ w["o"].T
 
 
@@ -122,6 +132,23 @@ def moe_ff(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping) -> torc
     return out
 
 
+def connected(X: List[torch.Tensor], a: torch.Tensor, M: torch.Tensor, b: torch.Tensor, fn) -> List[torch.Tensor]:
+    """One sublayer over n streams: u = sum_s a[s] X_s, y = fn(u), X_t <- sum_s M[s, t] X_s + b[t] y."""
+    n = len(X)
+    y = fn(sum(a[s] * X[s] for s in range(n)))
+    return [sum(M[s, t] * X[s] for s in range(n)) + b[t] * y for t in range(n)]
+
+
+def read_model_folder(folder: str):
+    """(config.json as a dict, tensors by name) of a model folder."""
+    import json
+    import os
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(folder, "model.safetensors"))
+
+
 def _sub(w: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:
     return {k[len(prefix):]: v for k, v in w.items() if k.startswith(prefix)}
 
@@ -140,12 +167,10 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[i
     kept: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
 
     def sublayer(X, q: int, p: str, fn):
+        norm = lambda u: rms_norm(u, w[f"{p}norm{q}"], eps)
         if not S:                                             # one stream: the plain residual sum
-            return [X[0] + fn(rms_norm(X[0], w[f"{p}norm{q}"], eps))]
-        a, b, M = w[f"{p}hc{q}.in"], w[f"{p}hc{q}.out"], w[f"{p}hc{q}.mix"]
-        u = sum(a[s] * X[s] for s in range(S))
-        y = fn(rms_norm(u, w[f"{p}norm{q}"], eps))
-        return [sum(M[s, t] * X[s] for s in range(S)) + b[t] * y for t in range(S)]
+            return [X[0] + fn(norm(X[0]))]
+        return connected(X, w[f"{p}hc{q}.in"], w[f"{p}hc{q}.mix"], w[f"{p}hc{q}.out"], lambda u: fn(norm(u)))
 
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
