@@ -17,9 +17,10 @@ attention), the Llama-3.2-3B-shaped model at 8 of its 28 layers serving 64 reque
 this engine's attention and GEMM kernels timed against the reference's own attention kernels
 (compiled unmodified, see baseline/reference_kernels.py) and the library GEMM on the same data.
 `--shape` takes the layer sizes of the 3B or 8B benchmark configuration for the headline instead;
-`--only decode|prefill|serve` runs one part alone and prints its time.  `--family dirurax` leaves all of that
-aside and prints a line of its own: prefill and decode of Dirurax models at two sizes beside Llama models of the
-same width, depth, feed-forward width and vocabulary, and that family's kernels alone against their rooflines.
+`--only decode|prefill|serve` runs one part alone and prints its time.  `--family dirurax` (or `pikalix`) leaves
+all of that aside and prints a line of its own: prefill and decode of that family's models at two sizes beside
+Llama models of the same width, depth, feed-forward width and vocabulary, and that family's kernels alone against
+their rooflines.
 """
 from __future__ import annotations
 
@@ -594,8 +595,163 @@ def dirurax_kernels(hbm_gbs, size):
     return out
 
 
+def _pikalix(width, layers, ff, vocab, attn, window, rot, experts, top, expert_ff, shared_ff, groups, streams):
+    """`layers` layers of attention with a sliding window; the second half reads the keys and values of the
+    last layer of the first half; feed-forwards alternate between a dense one and routed experts."""
+    h, kv, dim, vdim = attn
+    out = []
+    for i in range(layers):
+        mixer = {"heads": h, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window},
+                 "rot": {"dims": rot, "base": 500000.0}}
+        if i >= layers // 2:
+            mixer["kv_from"] = layers // 2 - 1
+        mlp = {"kind": "dense", "ff": ff} if i % 2 == 0 else {
+            "kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff},
+            "router": {"experts": experts, "top": top, "groups": {"count": groups[0], "keep": groups[1]}}}
+        out.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Pikalix", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "streams": streams, "layers": out}
+
+
+# Pikalix at the same widths: a token's feed-forward work equals the dense one's (top x expert_ff + shared_ff = ff)
+PIKALIX_SIZES = {
+    "w1024": dict(width=1024, layers=8, ff=4096, vocab=32768, attn=(16, 4, 64, 64), window=1024, rot=32, experts=32, top=4,
+                  expert_ff=768, shared_ff=1024, groups=(8, 4), streams=2, llama=(16, 4, 64)),
+    "w2048": dict(width=2048, layers=8, ff=8192, vocab=32768, attn=(32, 8, 64, 64), window=1024, rot=32, experts=32, top=4,
+                  expert_ff=1536, shared_ff=2048, groups=(8, 4), streams=2, llama=(32, 8, 64)),
+}
+
+
+def pikalix_kernels(hbm_gbs, bf16_tflops, size):
+    """The Pikalix kernels alone at one size, each beside the like kernel of the Llama path on the same shapes:
+    microseconds, and what that is of the bytes they must move at the measured copy bandwidth (or of the
+    measured library GEMM rate for the experts' products over a prompt)."""
+    import torch
+    from rustinfer_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    sz = PIKALIX_SIZES[size]
+    d, S = sz["width"], sz["streams"]
+    Hq, Hkv, hd, vd = sz["attn"]
+    E, top, fe = sz["experts"], sz["top"], sz["expert_ff"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)
+    frac = lambda moved, us: round(moved / (us * 1e-6) / 1e9 / hbm_gbs, 4)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    out = {}
+    for tag, T in (("prefill2048", 2048), ("decode64", 64)):
+        # the streams' update + weighted sum + norm beside the add + RMSNorm of one stream
+        X = torch.randn(S, T, d, device=dev)
+        y = torch.randn(T, d, device=dev)
+        mix, wr, rd = torch.randn(S, S, device=dev), torch.randn(S, device=dev), torch.randn(S, device=dev)
+        w = bf(d)
+        xo = torch.empty(T, d, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.hyper_collect(X, False, y, mix, wr, rd, w, 1e-6, xo), flush=flush)
+        h, delta = torch.randn(T, d, device=dev), bf(T, d)
+        us_rms = time_kernel(lambda: K.add_rmsnorm(h, delta, w, 1e-6, xo), flush=flush)
+        out[f"stream_norm_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * d * (8 * S + 4 + 2), us),
+                                     "add_rmsnorm_us": round(us_rms, 1), "add_rmsnorm_hbm_frac": frac(T * d * (4 + 4 + 2 + 2), us_rms)}
+        # q, k, v from the projection to the attention and the cache beside the rotary + cache-write kernel
+        cols = (Hq + Hkv) * hd + Hkv * vd
+        pages = T // PAGE + 1
+        cache = bf(pages, 2, Hkv, PAGE, hd)
+        qkv32, bias = torch.randn(T, cols, device=dev), torch.randn(cols, device=dev)
+        qw, kw = bf(Hq * hd), bf(Hkv * hd)
+        pos, slots = i32(list(range(T))), i32(list(range(T)))
+        cos, sin = torch.randn(T, sz["rot"] // 2, device=dev), torch.randn(T, sz["rot"] // 2, device=dev)
+        q_out = torch.empty(T, Hq * hd, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.qkv_prepare(qkv32, bias, qw, kw, 2, 1e-6, pos, cos, sin, sz["rot"], True, slots, cache, q_out,
+                                               Hq, Hkv, hd, vd, True), flush=flush)
+        qkv16 = bf(T, cols)
+        cos2, sin2 = torch.randn(T, hd // 2, device=dev), torch.randn(T, hd // 2, device=dev)
+        us_rope = time_kernel(lambda: K.rope_scatter(qkv16, pos, cos2, sin2, slots, cache, Hq, Hkv, hd, hd), flush=flush)
+        out[f"qkv_prepare_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * cols * (4 + 2), us),
+                                     "rope_scatter_us": round(us_rope, 1), "rope_scatter_hbm_frac": frac(T * cols * (2 + 2), us_rope)}
+        # the experts: choice and sort, the two products, the weighted sum
+        N = T * top
+        z, corr = torch.randn(T, E, device=dev), torch.randn(E, device=dev) * 0.1
+        ids = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, top, device=dev)
+        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        offsets, order, place = (torch.empty(n, dtype=torch.int32, device=dev) for n in (E + 1, N, N))
+
+        def choose():
+            counts.zero_()
+            K.moe_route(z, corr, top, sz["groups"][0], sz["groups"][1], False, ids, wts, counts)
+            K.moe_sort(ids, counts, offsets, order, place)
+        us = time_kernel(choose, flush=flush)
+        out[f"experts_choice_{tag}"] = {"us": round(us, 1), "launches": 2}
+        x = bf(T, d)
+        gate_up, down = bf(E, 2 * fe, d) * 0.02, bf(E, d, fe) * 0.02
+        mid = torch.empty(N, fe, device=dev, dtype=torch.bfloat16)
+        Y = torch.empty(N, d, device=dev)
+        us1 = time_kernel(lambda: K.moe_product(x, gate_up, mid, offsets, order, top, gated=True), flush=flush)
+        us2 = time_kernel(lambda: K.moe_product(mid, down, Y, offsets, None, top, gated=False), flush=flush)
+        used = int((counts > 0).sum())
+        flops = 2 * N * d * fe * 3
+        moved = used * 3 * fe * d * 2 + N * (d * 2 + fe * 4 + d * 4)
+        # the like work of the Llama path: one dense product pair over the same rows (N rows, the tcgen05 GEMM)
+        xd, wd1, wd2 = bf(N, d), bf(2 * fe, d) * 0.02, bf(d, fe) * 0.02
+        m2, y2 = torch.empty(N, fe, device=dev, dtype=torch.bfloat16), torch.empty(N, d, device=dev)
+        usd = time_kernel(lambda: (K.gemm_tc(xd, wd1, m2, K.EPI_SILU, num_sms=sms), K.gemm_tc(m2, wd2, y2, K.EPI_F32, num_sms=sms)),
+                          flush=flush)
+        out[f"experts_products_{tag}"] = {"us": round(us1 + us2, 1), "gate_up_us": round(us1, 1), "down_us": round(us2, 1),
+                                          "tflops": round(flops / ((us1 + us2) * 1e-6) / 1e12, 1),
+                                          "gemm_frac": round(flops / ((us1 + us2) * 1e-6) / 1e12 / bf16_tflops, 4),
+                                          "hbm_frac": frac(moved, us1 + us2), "experts_used": used,
+                                          "dense_pair_same_rows_us": round(usd, 1),
+                                          "dense_pair_tflops": round(flops / (usd * 1e-6) / 1e12, 1)}
+        shared = torch.randn(T, d, device=dev)
+        o = torch.empty(T, d, device=dev)
+        us = time_kernel(lambda: K.moe_combine(Y, place, wts, shared, o, counts), flush=flush)
+        out[f"experts_sum_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * d * (4 * top + 4 + 4), us)}
+    # attention: 64 single tokens at 4,096 keys of which the window keeps 1,024, beside the split-KV kernel with the same window
+    B, ctx, win = 64, 4096, sz["window"]
+    blocks = ctx // PAGE
+    cache = bf(B * blocks, 2, Hkv, PAGE, hd)
+    table = torch.randperm(B * blocks, device=dev).to(torch.int32).view(B, blocks).contiguous()
+    q, ao = bf(B, Hq * hd), torch.empty(B, Hq * vd, device=dev, dtype=torch.bfloat16)
+    kv_len, cu, ent = i32([ctx] * B), i32(list(range(B + 1))), i32(list(range(B)))
+    us = time_kernel(lambda: K.attention_single(q, ao, cache, table, cu, kv_len, ent, Hq, Hkv, hd, hd ** -0.5, win, None, vd, sink=True),
+                     flush=flush)
+    moved = B * Hkv * win * (hd + vd) * 2
+    from rustinfer_b200.parts.base import MIXERS, BuildContext
+    from rustinfer_b200.parts.spec import PartSpec
+    part = MIXERS.build(PartSpec("gqa_attention", {"hidden_size": 64, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd,
+                                                   "scale": hd ** -0.5, "window": win, "position": None}))
+    part.prepare(BuildContext(dev, torch.bfloat16, ctx, PAGE, max_batch_seqs=64, num_sms=sms))
+    splits = part._splits(B, ctx)
+    no, nl = K.decode_scratch_floats(B, Hq, hd, splits)
+    po, pl = torch.empty(no, device=dev), torch.empty(nl, device=dev)
+    us_d = time_kernel(lambda: K.attention_decode_bf16(q, ao, cache, table, cu, kv_len, None, B, Hq, Hkv, hd, hd ** -0.5, win,
+                                                       splits, po, pl), flush=flush)
+    out["window_attention_decode64"] = {"us": round(us, 1), "hbm_frac": frac(moved, us), "split_kv_us": round(us_d, 1),
+                                        "split_kv_hbm_frac": frac(moved, us_d)}
+    # a prompt of 2,048 tokens: fp32 softmax weights with the sink beside the tcgen05 kernel with the same window
+    T = 2048
+    tbl = table[:1, : T // PAGE].contiguous()
+    qp, op = bf(T, Hq * hd), torch.empty(T, Hq * vd, device=dev, dtype=torch.bfloat16)
+    cup, kvl = i32([0, T]), i32([T])
+    pairs = sum(min(p + 1, win) for p in range(T))
+    rows = K.mma_tokens_per_tile(Hq, Hkv)
+    tl = list(range(0, T, rows))
+    te, t0 = i32([0] * len(tl)), i32(tl)
+    us = time_kernel(lambda: K.attention_prefill_bf16(qp, op, cache, tbl, cup, kvl, te, t0, Hq, Hkv, hd, hd ** -0.5, win, None,
+                                                      precise=True, sink=True), flush=flush)
+    res = {"us": round(us, 1), "tflops": round(2 * pairs * Hq * (hd + 3 * vd) / (us * 1e-6) / 1e12, 2),
+           "useful_tflops": round(2 * pairs * Hq * (hd + vd) / (us * 1e-6) / 1e12, 2)}
+    if K.tc_attention_supports(Hq, Hkv, hd, PAGE):
+        rows = K.tc_tokens_per_tile(Hq, Hkv)
+        tl = list(range(0, T, rows))
+        te2, t02 = i32([0] * len(tl)), i32(tl)
+        us2 = time_kernel(lambda: K.attention_prefill_tc(qp, op, cache, tbl, cup, kvl, te2, t02, Hq, Hkv, hd, hd ** -0.5, win),
+                          flush=flush)
+        res.update(window_tc_us=round(us2, 1), window_tc_tflops=round(2 * pairs * Hq * 2 * hd / (us2 * 1e-6) / 1e12, 2))
+    out["window_attention_prefill2048"] = res
+    return out
+
+
 def family_bench(args) -> int:
-    """`--family dirurax`: prefill and decode throughput of Dirurax models at a few sizes beside
+    """`--family dirurax|pikalix`: prefill and decode throughput of that family's models at a few sizes beside
     Llama models of the same width, depth, feed-forward width and vocabulary (random weights), and the
     family's own kernels alone.  One JSON line."""
     import torch
@@ -607,13 +763,17 @@ def family_bench(args) -> int:
     windows = []
     say = lambda msg: print(f"[bench] {msg}", file=sys.stderr, flush=True)
     ctx, tokens = min(args.context, 4096), max(2, min(args.prompt_tokens, 8192))
-    result = {"family": "dirurax", "dtype": "bf16", "data": "synthetic", "peaks": peak_kind, "points": {}, "kernels": {}}
-    sizes = [s for s in FAMILY_SIZES if not args.size or s in args.size.split(",")]
+    family = args.family
+    table = PIKALIX_SIZES if family == "pikalix" else FAMILY_SIZES
+    result = {"family": family, "dtype": "bf16", "data": "synthetic", "peaks": peak_kind, "points": {}, "kernels": {}}
+    sizes = [s for s in table if not args.size or s in args.size.split(",")]
     for size in sizes:
-        sz = FAMILY_SIZES[size]
-        configs = {
-            "dirurax": _dirurax(sz["width"], sz["layers"], sz["ff"], sz["vocab"], sz["gla"], sz["attn"], sz["delta"], sz["block"]),
-            "llama": _llama_like(sz["width"], sz["layers"], sz["ff"], sz["vocab"], *sz["llama"])}
+        sz = table[size]
+        if family == "pikalix":
+            own = _pikalix(**{k: v for k, v in sz.items() if k != "llama"})
+        else:
+            own = _dirurax(sz["width"], sz["layers"], sz["ff"], sz["vocab"], sz["gla"], sz["attn"], sz["delta"], sz["block"])
+        configs = {family: own, "llama": _llama_like(sz["width"], sz["layers"], sz["ff"], sz["vocab"], *sz["llama"])}
         point = {}
         for fam, cfg in configs.items():
             with tempfile.TemporaryDirectory(prefix="rustinfer_b200_bench_") as tmp:
@@ -638,14 +798,15 @@ def family_bench(args) -> int:
                 say(f"{size} {fam}: prefill {tokens} tokens {ms_p:.3f} ms, decode b{args.batch} ctx{ctx} {ms_d:.4f} ms/step")
                 del engine
                 torch.cuda.empty_cache()
-        point["prefill_ratio"] = round(point["dirurax"]["prefill_tokens_per_s"] / point["llama"]["prefill_tokens_per_s"], 3)
-        point["decode_ratio"] = round(point["dirurax"]["decode_tokens_per_s"] / point["llama"]["decode_tokens_per_s"], 3)
+        point["prefill_ratio"] = round(point[family]["prefill_tokens_per_s"] / point["llama"]["prefill_tokens_per_s"], 3)
+        point["decode_ratio"] = round(point[family]["decode_tokens_per_s"] / point["llama"]["decode_tokens_per_s"], 3)
         result["points"][size] = point
-        result["kernels"][size] = dirurax_kernels(hbm_gbs, size)
+        result["kernels"][size] = (pikalix_kernels(hbm_gbs, bf16_tflops, size) if family == "pikalix"
+                                   else dirurax_kernels(hbm_gbs, size))
         say(f"{size} kernels: {result['kernels'][size]}")
     clocks.stop()
     result["config"] = {"batch": args.batch, "context": ctx, "prompt_tokens": tokens,
-                        "sizes": {s: {k: v for k, v in FAMILY_SIZES[s].items()} for s in sizes},
+                        "sizes": {s: {k: v for k, v in table[s].items()} for s in sizes},
                         "l2": "a 256 MB buffer is rewritten between timed kernel runs; model steps read weights larger than L2"}
     result["clocks"] = clocks.summary(windows)
     print(json.dumps(result))
@@ -675,10 +836,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: length of the prompt, computed in one step (up to 8192)")
-    ap.add_argument("--family", default="llama", choices=["llama", "dirurax"],
-                    help="dirurax: that family's prefill and decode at a few sizes beside Llama models of equal size, "
+    ap.add_argument("--family", default="llama", choices=["llama", "dirurax", "pikalix"],
+                    help="dirurax, pikalix: that family's prefill and decode at a few sizes beside Llama models of equal size, "
                          "and its kernels alone (one JSON line of its own; the default workload is unchanged)")
-    ap.add_argument("--size", default="", help="with --family dirurax: sizes to run, with commas (default: all)")
+    ap.add_argument("--size", default="", help="with --family dirurax or pikalix: sizes to run, with commas (default: all)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: --gpus {args.gpus} is not supported by this engine")
@@ -690,7 +851,7 @@ def main() -> int:
         return 0
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 2)
-    if args.family == "dirurax":
+    if args.family in ("dirurax", "pikalix"):
         return family_bench(args)
 
     import torch

@@ -233,6 +233,146 @@ moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict_
     }
 }
 
+// The same products for bf16 rows and matrices on the tensor cores (mma.sync m16n8k16, fp32 accumulation):
+// a CTA of four warps owns BM rows x 64 columns of one expert, a warp 16 of the columns; rows and matrix
+// rows arrive by cp.async in 16-byte pieces through a ring of three stages of 64 k each (the rows gathered
+// through `order`), fragments by ldmatrix from rows padded by 16 bytes.  K must be a multiple of 8 and the
+// rows 16-byte aligned; other shapes take the kernel above.
+constexpr int TBK = 64, TROW = TBK + 8, TSTAGES = 3;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;      // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int BM, bool GATED> constexpr size_t moe_mma_smem() {
+    return (size_t)TSTAGES * (BM + (GATED ? 2 : 1) * GBN) * TROW * sizeof(bf16);
+}
+
+template <typename TO, int BM, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_product_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w, TO* __restrict__ out,
+                       int out_stride, const int* __restrict__ offsets, const int* __restrict__ order, int top,
+                       int gather, int E, int N, int K) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int MB = BM / 16;                            // 16-row blocks
+    constexpr int NW = GATED ? 2 : 1;                      // matrices a tile reads
+    constexpr int STAGE = (BM + NW * GBN) * TROW;          // elements a stage
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sm = reinterpret_cast<bf16*>(smem_raw);
+    __shared__ int s_tile[3];
+    __shared__ int s_src[BM];                              // row of `a` behind every row of the tile (-1: none)
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, e = 0, row0 = 0, n_rows = 0;
+        for (; e < E; ++e) {
+            const int lo = offsets[e], cnt = offsets[e + 1] - lo;
+            const int tiles = (cnt + BM - 1) / BM;
+            if (tile < tiles) { row0 = lo + tile * BM; n_rows = min(BM, cnt - tile * BM); break; }
+            tile -= tiles;
+        }
+        s_tile[0] = e; s_tile[1] = row0; s_tile[2] = n_rows;
+    }
+    __syncthreads();
+    const int e = s_tile[0], row0 = s_tile[1], n_rows = s_tile[2];
+    if (e >= E || n_rows <= 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int r = tid; r < BM; r += 128) s_src[r] = r < n_rows ? (gather ? order[row0 + r] / top : row0 + r) : -1;
+    __syncthreads();
+    const int n0 = blockIdx.y * GBN;
+    const int Ntot = GATED ? 2 * N : N;
+    const bf16* we = w + (size_t)e * Ntot * K;
+    const int kblocks = (K + TBK - 1) / TBK;
+
+    auto load_stage = [&](int kb, int stage) {
+        bf16* As = sm + (size_t)stage * STAGE;
+        bf16* Ws = As + BM * TROW;
+        const int k0 = kb * TBK;
+        for (int c = tid; c < BM * (TBK / 8); c += 128) {
+            const int r = c >> 3, ch = c & 7;
+            const int src = s_src[r];
+            const bool ok = src >= 0 && k0 + ch * 8 < K;
+            cp_async16(As + r * TROW + ch * 8, ok ? a + (size_t)src * a_stride + k0 + ch * 8 : a, ok);
+        }
+        for (int c = tid; c < NW * GBN * (TBK / 8); c += 128) {
+            const int r = c >> 3, ch = c & 7;              // r: 0..63 first matrix, 64..127 second
+            const int half = r / GBN, col = r - half * GBN;
+            const bool ok = n0 + col < N && k0 + ch * 8 < K;
+            cp_async16(Ws + r * TROW + ch * 8, ok ? we + (size_t)(half * N + n0 + col) * K + k0 + ch * 8 : we, ok);
+        }
+    };
+
+    float acc[NW][MB][2][4];
+#pragma unroll
+    for (int h = 0; h < NW; ++h)
+#pragma unroll
+        for (int m = 0; m < MB; ++m)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) acc[h][m][j][0] = acc[h][m][j][1] = acc[h][m][j][2] = acc[h][m][j][3] = 0.f;
+
+#pragma unroll
+    for (int st = 0; st < TSTAGES - 1; ++st) {
+        if (st < kblocks) load_stage(st, st);
+        cp_async_commit();
+    }
+    for (int kb = 0; kb < kblocks; ++kb) {
+        cp_async_wait<TSTAGES - 2>();
+        __syncthreads();                                   // stage kb has landed; stage kb-1 is free for all
+        if (kb + TSTAGES - 1 < kblocks) load_stage(kb + TSTAGES - 1, (kb + TSTAGES - 1) % TSTAGES);
+        cp_async_commit();
+        const bf16* As = sm + (size_t)(kb % TSTAGES) * STAGE;
+        const bf16* Ws = As + BM * TROW;
+#pragma unroll
+        for (int ks = 0; ks < TBK / 16; ++ks) {
+            unsigned bfr[NW][4];
+#pragma unroll
+            for (int h = 0; h < NW; ++h)
+                ldmatrix_x4(bfr[h], Ws + (h * GBN + warp * 16 + (lane & 7) + (lane >> 4) * 8) * TROW + ks * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                unsigned af[4];
+                ldmatrix_x4(af, As + (m * 16 + (lane & 15)) * TROW + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int h = 0; h < NW; ++h) {
+                    mma_bf16(acc[h][m][0], af, bfr[h][0], bfr[h][1]);
+                    mma_bf16(acc[h][m][1], af, bfr[h][2], bfr[h][3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = m * 16 + (lane >> 2) + 8 * half;
+                if (r >= n_rows) continue;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int n = n0 + warp * 16 + j * 8 + (lane & 3) * 2 + c;
+                    if (n >= N) continue;
+                    float v = acc[0][m][j][2 * half + c];
+                    if (GATED) v = v / (1.0f + __expf(-v)) * acc[NW - 1][m][j][2 * half + c];
+                    out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v);
+                }
+            }
+}
+
 // ------------------------------------------------------------------------------ combine
 // out[t][c] = sum_j weights[t][j] * Y[place[t*top + j]][c] (+ shared[t][c]), j = 0, 1, .. in that order.
 template <typename TS, typename TO>
@@ -276,6 +416,13 @@ RI_API int ri_moe_sort(const int* ids, const int* counts, int N, int E, int* off
 
 RI_API int ri_moe_product_rows(int rows, int E) { return rows / E >= 24 ? 64 : 16; }
 
+// 1 (default): bf16 products on the tensor cores; 0: the fp32 multiply-add kernel for every dtype.
+static int& ri_moe_tensor_cores() {
+    static int on = 1;
+    return on;
+}
+RI_API void ri_moe_set_tensor_cores(int on) { ri_moe_tensor_cores() = on ? 1 : 0; }
+
 // a_dtype / w_dtype / out_dtype: RI_F32 or RI_BF16.  rows: T * top (the pairs).  gated: see the kernel.
 RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* w, int w_dtype, void* out, int out_dtype,
                           int out_stride, const int* offsets, const int* order, int top, int gather, int rows, int E,
@@ -287,6 +434,23 @@ RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* 
 #define RI_MP(TA, TW, TO, BM, G) RI_CHECKED(ri_launch(moe_product_kernel<TA, TW, TO, BM, G>, grid, dim3(256), 0, s, (const TA*)a, \
         a_stride, (const TW*)w, (TO*)out, out_stride, offsets, order, top, gather, E, N, K))
 #define RI_MP_BM(TA, TW, TO, G) do { if (bm == 64) RI_MP(TA, TW, TO, 64, G); else RI_MP(TA, TW, TO, 16, G); } while (0)
+    const bool tensor_cores = a_dtype == RI_BF16 && w_dtype == RI_BF16 && K % 8 == 0 && a_stride % 8 == 0 &&
+                              ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ri_moe_tensor_cores();
+    if (tensor_cores && ((gated && out_dtype == RI_BF16) || (!gated && out_dtype == RI_F32))) {
+#define RI_MM(TO, BM, G) do { \
+        static bool configured = false; \
+        const size_t smem = moe_mma_smem<BM, G>(); \
+        if (!configured) { \
+            cudaError_t ce = cudaFuncSetAttribute(moe_product_mma_kernel<TO, BM, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (ce != cudaSuccess) return (int)ce; \
+            configured = true; } \
+        RI_CHECKED(ri_launch(moe_product_mma_kernel<TO, BM, G>, grid, dim3(128), smem, s, (const bf16*)a, a_stride, (const bf16*)w, \
+            (TO*)out, out_stride, offsets, order, top, gather, E, N, K)); } while (0)
+        if (gated) { if (bm == 64) RI_MM(bf16, 64, true); else RI_MM(bf16, 16, true); }
+        else { if (bm == 64) RI_MM(float, 64, false); else RI_MM(float, 16, false); }
+#undef RI_MM
+        return ri_launch_status();
+    }
     if (a_dtype == RI_BF16 && w_dtype == RI_BF16 && out_dtype == RI_BF16 && gated) RI_MP_BM(bf16, bf16, bf16, true);
     else if (a_dtype == RI_BF16 && w_dtype == RI_BF16 && out_dtype == RI_F32 && !gated) RI_MP_BM(bf16, bf16, float, false);
     else if (a_dtype == RI_F32 && w_dtype == RI_F32 && out_dtype == RI_F32 && gated) RI_MP_BM(float, float, float, true);
