@@ -668,7 +668,7 @@ def pikalix_kernels(hbm_gbs, bf16_tflops, size):
                                      "rope_scatter_us": round(us_rope, 1), "rope_scatter_hbm_frac": frac(T * cols * (2 + 2), us_rope)}
         # the experts: choice and sort, the two products, the weighted sum
         N = T * top
-        z, corr = torch.randn(T, E, device=dev), torch.randn(E, device=dev) * 0.1
+        xr, rw, corr = bf(T, d), torch.randn(E, d, device=dev) * 0.02, torch.randn(E, device=dev) * 0.1
         ids = torch.empty(T, top, dtype=torch.int32, device=dev)
         wts = torch.empty(T, top, device=dev)
         counts = torch.zeros(E, dtype=torch.int32, device=dev)
@@ -676,7 +676,7 @@ def pikalix_kernels(hbm_gbs, bf16_tflops, size):
 
         def choose():
             counts.zero_()
-            K.moe_route(z, corr, top, sz["groups"][0], sz["groups"][1], False, ids, wts, counts)
+            K.moe_route(None, corr, top, sz["groups"][0], sz["groups"][1], False, ids, wts, counts, x=xr, router=rw)
             K.moe_sort(ids, counts, offsets, order, place)
         us = time_kernel(choose, flush=flush)
         out[f"experts_choice_{tag}"] = {"us": round(us, 1), "launches": 2}
@@ -684,9 +684,16 @@ def pikalix_kernels(hbm_gbs, bf16_tflops, size):
         gate_up, down = bf(E, 2 * fe, d) * 0.02, bf(E, d, fe) * 0.02
         mid = torch.empty(N, fe, device=dev, dtype=torch.bfloat16)
         Y = torch.empty(N, d, device=dev)
+        used = int((offsets[1:] > offsets[:-1]).sum())
         us1 = time_kernel(lambda: K.moe_product(x, gate_up, mid, offsets, order, top, gated=True), flush=flush)
         us2 = time_kernel(lambda: K.moe_product(mid, down, Y, offsets, None, top, gated=False), flush=flush)
-        used = int((counts > 0).sum())
+        mma_us = us1 + us2
+        tensor_memory = N >= 24 * E                      # what the experts part does from that many rows on
+        if tensor_memory:
+            xs = torch.empty(N, d, device=dev, dtype=torch.bfloat16)
+            us0 = time_kernel(lambda: K.moe_gather(x, order, top, xs), flush=flush)
+            us1 = time_kernel(lambda: K.gemm_tc_grouped(xs, gate_up, mid, offsets, K.EPI_SILU), flush=flush) + us0
+            us2 = time_kernel(lambda: K.gemm_tc_grouped(mid, down, Y, offsets, K.EPI_F32), flush=flush)
         flops = 2 * N * d * fe * 3
         moved = used * 3 * fe * d * 2 + N * (d * 2 + fe * 4 + d * 4)
         # the like work of the Llama path: one dense product pair over the same rows (N rows, the tcgen05 GEMM)
@@ -698,6 +705,8 @@ def pikalix_kernels(hbm_gbs, bf16_tflops, size):
                                           "tflops": round(flops / ((us1 + us2) * 1e-6) / 1e12, 1),
                                           "gemm_frac": round(flops / ((us1 + us2) * 1e-6) / 1e12 / bf16_tflops, 4),
                                           "hbm_frac": frac(moved, us1 + us2), "experts_used": used,
+                                          "kernel": "tcgen05 (gather + two grouped products)" if tensor_memory else "mma.sync",
+                                          "mma_sync_us": round(mma_us, 1),
                                           "dense_pair_same_rows_us": round(usd, 1),
                                           "dense_pair_tflops": round(flops / (usd * 1e-6) / 1e12, 1)}
         shared = torch.randn(T, d, device=dev)
@@ -711,11 +720,16 @@ def pikalix_kernels(hbm_gbs, bf16_tflops, size):
     table = torch.randperm(B * blocks, device=dev).to(torch.int32).view(B, blocks).contiguous()
     q, ao = bf(B, Hq * hd), torch.empty(B, Hq * vd, device=dev, dtype=torch.bfloat16)
     kv_len, cu, ent = i32([ctx] * B), i32(list(range(B + 1))), i32(list(range(B)))
-    us = time_kernel(lambda: K.attention_single(q, ao, cache, table, cu, kv_len, ent, Hq, Hkv, hd, hd ** -0.5, win, None, vd, sink=True),
-                     flush=flush)
-    moved = B * Hkv * win * (hd + vd) * 2
     from rustinfer_b200.parts.base import MIXERS, BuildContext
     from rustinfer_b200.parts.spec import PartSpec
+    own = MIXERS.build(PartSpec("gqa_attention", {"hidden_size": 64, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd,
+                                                  "value_dim": vd, "scale": hd ** -0.5, "window": win, "position": None,
+                                                  "sink": True}))
+    own.prepare(BuildContext(dev, torch.bfloat16, ctx, PAGE, max_batch_seqs=64, num_sms=sms))
+    ranges = own._single_splits(B, ctx)
+    us = time_kernel(lambda: K.attention_single(q, ao, cache, table, cu, kv_len, ent, Hq, Hkv, hd, hd ** -0.5, win, None, vd,
+                                                sink=True, splits=ranges, part=own.single_part), flush=flush)
+    moved = B * Hkv * win * (hd + vd) * 2
     part = MIXERS.build(PartSpec("gqa_attention", {"hidden_size": 64, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd,
                                                    "scale": hd ** -0.5, "window": win, "position": None}))
     part.prepare(BuildContext(dev, torch.bfloat16, ctx, PAGE, max_batch_seqs=64, num_sms=sms))
@@ -724,7 +738,7 @@ def pikalix_kernels(hbm_gbs, bf16_tflops, size):
     po, pl = torch.empty(no, device=dev), torch.empty(nl, device=dev)
     us_d = time_kernel(lambda: K.attention_decode_bf16(q, ao, cache, table, cu, kv_len, None, B, Hq, Hkv, hd, hd ** -0.5, win,
                                                        splits, po, pl), flush=flush)
-    out["window_attention_decode64"] = {"us": round(us, 1), "hbm_frac": frac(moved, us), "split_kv_us": round(us_d, 1),
+    out["window_attention_decode64"] = {"us": round(us, 1), "ranges": ranges, "hbm_frac": frac(moved, us), "split_kv_us": round(us_d, 1),
                                         "split_kv_hbm_frac": frac(moved, us_d)}
     # a prompt of 2,048 tokens: fp32 softmax weights with the sink beside the tcgen05 kernel with the same window
     T = 2048

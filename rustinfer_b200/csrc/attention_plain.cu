@@ -174,7 +174,10 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
 // (fp32 throughout): a thread a key for the scores (q in shared memory, a key element serves all G
 // heads), a warp a head for the chunk's maximum and weights, a warp a key and a lane a value channel
 // for the weighted sum, the warps' parts added at the end.  Same mask as above: keys lo .. p with
-// lo the later of the window's and the block's start.
+// lo the later of the window's and the block's start.  With gridDim.z > 1 the keys lo .. p are cut into that
+// many ranges, a CTA each, which leave their maximum, sum and unnormalised weighted sum in `part`
+// ([entry][head][range][VD + 2] fp32: the sums' VD values, then maximum and sum); the merge kernel below
+// joins them (and adds the sink there).
 constexpr int SK = 512;                        // keys per chunk
 constexpr int SG = 16;                         // most query heads a kv head
 constexpr int SV = (VD + 31) / 32;             // value channels a lane
@@ -186,7 +189,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
                         const T* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                         const int* __restrict__ entry_list, int Hq, int Hkv, int page_size, float scale,
-                        int window, int block, int sink) {
+                        int window, int block, int sink, float* __restrict__ part) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -202,9 +205,17 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     if (b < 0) return;
     const int t = cu_q[b];
     if (cu_q[b + 1] - t != 1) return;
-    const int p = kv_len[b] - 1;
+    int p = kv_len[b] - 1;
     int lo = window > 0 ? max(0, p - window + 1) : 0;
     if (block > 0) lo = max(lo, (p / block) * block);
+    const int splits = gridDim.z;
+    if (splits > 1) {
+        // this CTA's range of the keys, a multiple of 64 long; it may be empty
+        const int per = ((p - lo + 1 + splits - 1) / splits + 63) & ~63;
+        lo += blockIdx.z * per;
+        p = min(p, lo + per - 1);
+        sink = 0;                                        // the merge adds it once
+    }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int WARPS = THREADS / 32;
     for (int e = tid; e < G * HD; e += THREADS)
@@ -315,7 +326,44 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
         float total = 0.f;
         for (int w = 0; w < WARPS; ++w) total += red[((size_t)w * SG + g) * VD + d];
         const float l = lrun[g];
-        out[(size_t)t * out_stride + (size_t)(kvh * G + g) * VD + d] = from_f32<T>(l > 0.f ? total / l : 0.f);
+        if (splits > 1) {
+            float* dst = part + (((size_t)blockIdx.y * Hq + kvh * G + g) * splits + blockIdx.z) * (VD + 2);
+            dst[d] = total;
+            if (d == 0) { dst[VD] = mrun[g]; dst[VD + 1] = l; }
+        } else {
+            out[(size_t)t * out_stride + (size_t)(kvh * G + g) * VD + d] = from_f32<T>(l > 0.f ? total / l : 0.f);
+        }
+    }
+}
+
+// Joins the ranges of one (entry, head): M = the largest maximum (0 with the sink), L = sum l_z e^(m_z - M)
+// (+ e^(-M) for the sink), out = sum acc_z e^(m_z - M) / L.  Ranges in their order, so the sum is the same
+// whatever else runs.
+template <typename T>
+__global__ void attention_single_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride,
+                                              const int* __restrict__ cu_q, const int* __restrict__ entry_list,
+                                              int Hq, int splits, int sink) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = entry_list[blockIdx.y], h = blockIdx.x;
+    if (b < 0) return;
+    const int t = cu_q[b];
+    if (cu_q[b + 1] - t != 1) return;
+    const float* src = part + ((size_t)blockIdx.y * Hq + h) * splits * (VD + 2);
+    float M = sink ? 0.f : -INFINITY;
+    for (int z = 0; z < splits; ++z) M = fmaxf(M, src[(size_t)z * (VD + 2) + VD]);
+    float L = sink ? expf(-M) : 0.f;
+    for (int z = 0; z < splits; ++z) {
+        const float m = src[(size_t)z * (VD + 2) + VD];
+        if (m != -INFINITY) L += src[(size_t)z * (VD + 2) + VD + 1] * expf(m - M);
+    }
+    for (int d = threadIdx.x; d < VD; d += blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < splits; ++z) {
+            const float m = src[(size_t)z * (VD + 2) + VD];
+            if (m != -INFINITY) acc = fmaf(src[(size_t)z * (VD + 2) + d], expf(m - M), acc);
+        }
+        out[(size_t)t * out_stride + (size_t)h * VD + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
     }
 }
 
@@ -365,18 +413,20 @@ RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_st
 }
 
 // Entries that bring a single token (entry_list[i], -1: skip): keys and values of a kv head are read once
-// for its query heads.  Returns cudaErrorNotSupported for more than 16 query heads a kv head or values
+// for its query heads.  splits > 1: every entry's keys in that many ranges (a CTA each) through `part`, fp32
+// [n_entries][Hq][splits][VD + 2], and a second launch that joins them.  Returns cudaErrorNotSupported for more than 16 query heads a kv head or values
 // wider than 128 (the caller then uses the tiled kernel above, which takes everything).
 RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_stride, const void* cache, int dtype,
                                const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                const int* entry_list, int n_entries, int Hq, int Hkv, int page_size, float scale,
-                               int window, int block, int sink, void* stream) {
+                               int window, int block, int sink, int splits, float* part, void* stream) {
     if (n_entries <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
     if (Hq / Hkv > SG || SV > 4) return (int)cudaErrorNotSupported;
+    if (splits < 1 || splits > 64 || (splits > 1 && !part)) return (int)cudaErrorInvalidValue;
     const size_t smem = SINGLE_SMEM_FLOATS * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(Hkv, n_entries);
+    dim3 grid(Hkv, n_entries, splits);
 #define RI_SINGLE(T) do { static bool configured = false; \
     if (!configured) { \
         cudaError_t e = cudaFuncSetAttribute(attention_single_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -384,7 +434,9 @@ RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_s
         configured = true; } \
     RI_CHECKED(ri_launch(attention_single_kernel<T>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (T*)out, \
         out_stride, (const T*)cache, block_table, table_stride, cu_q, kv_len, entry_list, Hq, Hkv, page_size, scale, \
-        window, block, sink)); } while (0)
+        window, block, sink, part)); \
+    if (splits > 1) RI_CHECKED(ri_launch(attention_single_merge_kernel<T>, dim3(Hq, n_entries), dim3(VD < 64 ? 32 : 64), 0, s, \
+        (const float*)part, (T*)out, out_stride, cu_q, entry_list, Hq, splits, sink)); } while (0)
     if (dtype == RI_BF16) RI_SINGLE(bf16);
     else RI_SINGLE(float);
 #undef RI_SINGLE

@@ -90,7 +90,34 @@ struct Params {
     const int* rope_slot;                // [tokens] slot of the token's key in the cache, < 0: none; null: no keys
     bf16* rope_cache;                    // [page][K|V][kv head][slot][head_dim]
     int rope_hq, rope_hkv, rope_hd, rope_page;
+    // Grouped (one-CTA kernel, activations on the 128-row side): the rows of A belong to `grp_experts` groups
+    // in a row, group e the rows grp_offsets[e] .. grp_offsets[e + 1] - 1 (device memory, written by an earlier
+    // kernel), and meet the matrix of their own group: rows e * b_rows .. of B.  Tiles are numbered (row tile
+    // of a group) * grp_tiles_b + column tile over an upper bound of row tiles; numbers beyond the last are
+    // skipped by every role alike.  null: one matrix for all rows.
+    const int* grp_offsets;
+    int grp_experts, grp_tiles_b;
 };
+
+// Tile `tile` of a grouped product: first row and end of its group's rows, row of B its columns start at,
+// first feature.  False: there is no such tile.
+template <int BN>
+__device__ __forceinline__ bool grouped_tile(const Params& p, int tile, int& a0, int& a_end, int& bw0, int& feat0) {
+    int mt = tile / p.grp_tiles_b;
+    const int nt = tile - mt * p.grp_tiles_b;
+    int lo = p.grp_offsets[0];
+    for (int e = 0; e < p.grp_experts; ++e) {
+        const int hi = p.grp_offsets[e + 1];
+        const int tiles = (hi - lo + BM - 1) / BM;
+        if (mt < tiles) {
+            a0 = lo + mt * BM; a_end = hi; feat0 = nt * BN; bw0 = e * p.b_rows + feat0;
+            return true;
+        }
+        mt -= tiles;
+        lo = hi;
+    }
+    return false;
+}
 
 
 // one accumulator value: token `tok`, feature `feat` (neighbour: the value of feature feat + 1)
@@ -242,8 +269,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int woff = p.swap ? 0 : p.a_box * BK * 2, xoff = p.swap ? p.a_box * BK * 2 : 0;
         const unsigned stage_tx = (unsigned)(p.a_box + BN) * BK * 2;   // bytes the two boxes of a stage bring
         pdl_trigger();
-        const int pre = blockIdx.x < p.n_tiles ? min(n_kb, STAGES) : 0;
-        {
+        // (a grouped product's first tile is known only after the wait: its offsets come from the kernel before)
+        const int pre = (blockIdx.x < p.n_tiles && !p.grp_offsets) ? min(n_kb, STAGES) : 0;
+        if (pre > 0) {
             const int tile = blockIdx.x;
             const int w0 = p.swap ? (tile % p.tiles_a) * p.a_box : (tile / p.tiles_a) * BN;
             for (int i = 0; i < pre; ++i) {
@@ -259,7 +287,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int it = 0, s = 0;                                // k-blocks loaded so far, over all tiles; ring position
         unsigned par = 1;                                 // parity of the release the current lap of the ring waits for
         for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
-            const int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
+            int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
+            if (p.grp_offsets) {
+                int a_end, feat0;
+                if (!grouped_tile<BN>(p, tile, a0, a_end, b0, feat0)) continue;
+            }
             const int w0 = p.swap ? a0 : b0, x0 = p.swap ? b0 : a0;
             for (int i = 0; i < n_kb; ++i, ++it) {
                 unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
@@ -289,6 +321,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int s = 0, t = 0;
         unsigned par = 0;
         for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x, ++t) {
+            if (p.grp_offsets) {
+                int ga0, ga_end, gb0, gfeat0;
+                if (!grouped_tile<BN>(p, tile, ga0, ga_end, gb0, gfeat0)) { --t; continue; }    // no accumulator is used
+            }
             const int buf = t & 1, use = t >> 1;
             // the epilogue has emptied this accumulator (first use of a buffer passes at once)
             if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
@@ -322,9 +358,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         pdl_wait();                                       // out, workspace and counters belong to earlier kernels till now
         const bool atomic_out = p.splits > 1 && p.epilogue == EPI_RESIDUAL;
         for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++t) {
-            const int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
-            // lanes beyond the rows this tile loaded hold nothing of this tile
-            const int ra = quarter * 32 + lane < p.a_box ? a0 + quarter * 32 + lane : 0x3fffffff;
+            int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
+            int a_end = 0x3fffffff;
+            if (p.grp_offsets) {
+                int bw0;
+                if (!grouped_tile<BN>(p, tile, a0, a_end, bw0, b0)) { --t; continue; }
+            }
+            // lanes beyond the rows this tile loaded (or, grouped, beyond its group's rows) hold nothing of this tile
+            const int ra = (quarter * 32 + lane < p.a_box && a0 + quarter * 32 + lane < a_end) ? a0 + quarter * 32 + lane : 0x3fffffff;
             const int buf = t & 1, use = t >> 1;
             // (also for a K slice that got no k-block: the MMA thread commits at once, but it must
             // have passed its own wait on `acc_empty` before these warps arrive there, or it would
@@ -920,6 +961,7 @@ int gemm_tc_impl(const void* X, const void* W, int M, int N, int K, void* out, i
     p.sk_tiles = p.sk_pairs = p.sk_q = p.sk_extra = 0; p.sk_acc = nullptr;
     p.rope_positions = nullptr; p.rope_cos = p.rope_sin = nullptr; p.rope_slot = nullptr; p.rope_cache = nullptr;
     p.rope_hq = p.rope_hkv = p.rope_hd = p.rope_page = 0;
+    p.grp_offsets = nullptr; p.grp_experts = p.grp_tiles_b = 0;
     if (rope) {
         p.rope_positions = rope->rope_positions; p.rope_cos = rope->rope_cos; p.rope_sin = rope->rope_sin;
         p.rope_slot = rope->rope_slot; p.rope_cache = rope->rope_cache;
@@ -1031,6 +1073,54 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     if (epilogue == EPI_ROPE) return (int)cudaErrorInvalidValue;       // has an entry of its own
     return gemm_tc_impl(X, W, M, N, K, out, ld_out, epilogue, swap, bn, splits, a_box, workspace, counters, error,
                         sk_acc, nullptr, stream);
+}
+
+// Rows in groups, every group against a matrix of its own: X [rows][K] bf16 holds the groups one after the other,
+// group e the rows offsets[e] .. offsets[e + 1] - 1 (int32 [experts + 1] in device memory; the host never reads
+// it), W [experts][N][K] bf16.  out [rows][ld_out]: EPI_F32 or EPI_BF16 store X_e W_e^T; EPI_SILU stores
+// silu(gate) * up of matrices whose rows alternate gate_j, up_j into [rows][N / 2].  The grid covers
+// ceil(rows / 128) + experts row tiles; tiles that do not exist are skipped.
+RI_API int ri_gemm_tc_grouped(const void* X, const void* W, int rows, int N, int K, void* out, int ld_out, int epilogue,
+                              const int* offsets, int experts, int* error, void* stream) {
+    if (rows <= 0 || N <= 0 || experts <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || !error || !offsets || (epilogue != EPI_F32 && epilogue != EPI_BF16 && epilogue != EPI_SILU) ||
+        (epilogue == EPI_SILU && N % 2))
+        return (int)cudaErrorInvalidValue;
+    Params p;
+    p.pair_bn = 0;
+    p.sk_tiles = p.sk_pairs = p.sk_q = p.sk_extra = 0; p.sk_acc = nullptr;
+    p.rope_positions = nullptr; p.rope_cos = p.rope_sin = nullptr; p.rope_slot = nullptr; p.rope_cache = nullptr;
+    p.rope_hq = p.rope_hkv = p.rope_hd = p.rope_page = 0;
+    p.a_rows = rows; p.b_rows = N; p.K = K; p.swap = 0; p.epilogue = epilogue; p.out = out; p.ld_out = ld_out;
+    p.splits = 1; p.workspace = nullptr; p.counters = nullptr; p.error = error;
+    const int bn = N >= 256 ? 256 : N > 64 ? 128 : N > 32 ? 64 : N > 16 ? 32 : 16;
+    p.grp_offsets = offsets; p.grp_experts = experts; p.grp_tiles_b = (N + bn - 1) / bn;
+    p.tiles_a = (rows + BM - 1) / BM + experts;
+    p.n_tiles = p.tiles_a * p.grp_tiles_b;
+    const int esize = (epilogue == EPI_BF16 || epilogue == EPI_SILU) ? 2 : 4;
+    p.vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && ((size_t)ld_out * esize) % 16 == 0) ? 1 : 0;
+    p.a_box = BM;
+    p.stage_bytes = (BM + bn) * BK * 2;
+    p.budget = SMEM_BUDGET;
+    p.stages = p.budget / p.stage_bytes;
+    if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+    p.stages &= ~1;
+    if (p.stages < 2) return (int)cudaErrorInvalidValue;
+    CUtensorMap ma, mb;
+    int st = make_map(X, rows, K, BM, &ma);
+    if (st != 0) return st;
+    if ((long long)experts * N > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    st = make_map(W, experts * N, K, bn, &mb);
+    if (st != 0) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (bn) {
+        case 16: return launch<16>(ma, mb, p, p.n_tiles, s);
+        case 32: return launch<32>(ma, mb, p, p.n_tiles, s);
+        case 64: return launch<64>(ma, mb, p, p.n_tiles, s);
+        case 128: return launch<128>(ma, mb, p, p.n_tiles, s);
+        case 256: return launch<256>(ma, mb, p, p.n_tiles, s);
+    }
+    return (int)cudaErrorInvalidValue;
 }
 
 // q, k, v of many tokens with the rotary encoding and the cache write in the product's epilogue

@@ -3,7 +3,8 @@
 // count on the host: every launch has a grid that covers the worst case and finds its work in the offsets
 // the sort left on the device, so a step of these kernels can be captured in a CUDA graph.
 //
-//   route    z [T][E] fp32 router logits -> ids [T][top], weights [T][top] fp32, counts[e] += 1
+//   route    x [T][d], router matrix [E][d] fp32 -> logits z = W x in fp32 -> ids [T][top], weights [T][top] fp32,
+//            counts[e] += 1 (or from given logits z [T][E])
 //   sort     ids, counts -> offsets [E+1], order [T*top] (pairs in expert order, stable), place [T*top]
 //   products rows of an expert times that expert's matrix (fp32 sums in a fixed order of k)
 //   combine  y[t] = sum_j weight[t][j] * Y[place[t*top + j]] (+ shared[t]); counts put back to zero
@@ -12,7 +13,9 @@
 namespace {
 
 // ------------------------------------------------------------------------------- router
-// One warp a token.  score s = sigmoid(z); choice c = s + correction.  With groups: the experts form
+// One CTA a token.  Logit z_e = sum_i W[e][i] x[i] in fp32 (a lane every 32nd term, then a butterfly over the
+// lanes: the same order whatever else is in the batch) unless the logits are given; then one warp chooses.  score s = sigmoid(z);
+// choice c = s + correction.  With groups: the experts form
 // n_groups equal groups of neighbours, a group's score is the sum of its two largest c, and only
 // experts of the `keep` best groups can be chosen (the others count as -inf).  The `top` largest c are
 // chosen, the lowest index among equals; their weights are the s (divided by their sum when renorm).
@@ -25,20 +28,48 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
     }
 }
 
-__global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int T, int E,
-                                 int top, int n_groups, int keep, int renorm, int* __restrict__ ids,
-                                 float* __restrict__ weights, int* __restrict__ counts) {
+constexpr int ROUTE_WARPS = 4, ROUTE_CHUNK = 8;
+
+template <typename TX>
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_route_kernel(const float* __restrict__ z, const TX* __restrict__ x, const float* __restrict__ router,
+                 int d, const float* __restrict__ correction, int T, int E,
+                 int top, int n_groups, int keep, int renorm, int* __restrict__ ids,
+                 float* __restrict__ weights, int* __restrict__ counts) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm[];
-    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * warps + warp;
-    if (t >= T) return;
-    float* s = sm + (size_t)warp * (2 * E + n_groups);     // [E] scores
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    float* s = sm;                                         // [E] scores
     float* c = s + E;                                      // [E] choice scores
     float* gs = c + E;                                     // [n_groups] group scores
+    if (x) {
+        // the logits: the warps share the experts, eight at a time; a lane takes every 32nd term of all eight
+        // sums (x is read once for them), then the lanes' parts meet in a butterfly
+        const TX* xr = x + (size_t)t * d;
+        for (int e0 = warp * ROUTE_CHUNK; e0 < E; e0 += ROUTE_WARPS * ROUTE_CHUNK) {
+            float acc[ROUTE_CHUNK];
+#pragma unroll
+            for (int j = 0; j < ROUTE_CHUNK; ++j) acc[j] = 0.f;
+#pragma unroll 4
+            for (int i = lane; i < d; i += 32) {
+                const float xv = to_f32<TX>(xr[i]);
+#pragma unroll
+                for (int j = 0; j < ROUTE_CHUNK; ++j)
+                    if (e0 + j < E) acc[j] = fmaf(xv, router[(size_t)(e0 + j) * d + i], acc[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < ROUTE_CHUNK; ++j) {
+                const float dot = warp_sum(acc[j]);
+                if (lane == 0 && e0 + j < E) s[e0 + j] = dot;
+            }
+        }
+        __syncthreads();
+    }
+    if (warp != 0) return;                                 // the choice is one warp's work
     for (int e = lane; e < E; e += 32) {
-        const float sc = 1.0f / (1.0f + expf(-z[(size_t)t * E + e]));
+        const float sc = 1.0f / (1.0f + expf(-(x ? s[e] : z[(size_t)t * E + e])));
         s[e] = sc;
         c[e] = sc + (correction ? correction[e] : 0.f);
     }
@@ -141,7 +172,7 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, const int* __restri
 // ------------------------------------------------------------------------ experts' products
 // Rows in expert order: row p of the product belongs to expert e with offsets[e] <= p < offsets[e+1].
 // A [.., K]: row of place p is a[order[p] / top] when `gather`, else a[p].  W [E][Ntot][K].
-//   GATED: Ntot = 2 N, out[p][n] = silu(A.W[e][n]) * (A.W[e][N + n])   (n < N)
+//   GATED: Ntot = 2 N, the matrix's rows alternate gate_n, up_n: out[p][n] = silu(A.W[e][2n]) * (A.W[e][2n + 1])
 //   else:  Ntot = N,   out[p][n] = A.W[e][n]
 // Every sum runs over k = 0, 1, .. in that order with fp32 multiply-adds, so an output does not depend on
 // which rows share its tile.  A CTA of 256 threads owns BM x BN outputs of one expert; the grid's x covers
@@ -157,8 +188,9 @@ moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict_
     pdl_wait();
     constexpr int RM = BM / 16;                            // rows a thread: 16 thread rows
     constexpr int RN = GBN / 16;                           // columns a thread: 16 thread columns
+    static_assert(RN == 4, "a thread's four columns are two adjacent pairs");
     __shared__ float As[BM][GBK + 1];
-    __shared__ float Ws[GATED ? 2 : 1][GBN][GBK + 1];
+    __shared__ float Ws[GBN][GBK + 1];
     __shared__ int s_tile[3];                              // expert, first row, rows
     if (threadIdx.x == 0) {
         int tile = blockIdx.x, e = 0, row0 = 0, n_rows = 0;
@@ -173,17 +205,16 @@ moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict_
     __syncthreads();
     const int e = s_tile[0], row0 = s_tile[1], n_rows = s_tile[2];
     if (e >= E || n_rows <= 0) return;
-    const int n0 = blockIdx.y * GBN;
+    const int n0 = blockIdx.y * GBN;                       // first row of the matrix (of Ntot) this tile covers
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int Ntot = GATED ? 2 * N : N;
     const TW* we = w + (size_t)e * Ntot * K;
-    float acc[GATED ? 2 : 1][RM][RN];
+    // a thread's columns: the pairs (2 tx, 2 tx + 1) and (32 + 2 tx, 33 + 2 tx): a gate sits beside its up
+    float acc[RM][RN];
 #pragma unroll
-    for (int h = 0; h < (GATED ? 2 : 1); ++h)
+    for (int i = 0; i < RM; ++i)
 #pragma unroll
-        for (int i = 0; i < RM; ++i)
-#pragma unroll
-            for (int j = 0; j < RN; ++j) acc[h][i][j] = 0.f;
+        for (int j = 0; j < RN; ++j) acc[i][j] = 0.f;
     for (int k0 = 0; k0 < K; k0 += GBK) {
         for (int idx = tid; idx < BM * GBK; idx += 256) {
             const int r = idx / GBK, kk = idx - r * GBK;
@@ -197,9 +228,8 @@ moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict_
         }
         for (int idx = tid; idx < GBN * GBK; idx += 256) {
             const int c = idx / GBK, kk = idx - c * GBK;
-            const bool ok = n0 + c < N && k0 + kk < K;
-            Ws[0][c][kk] = ok ? to_f32<TW>(we[(size_t)(n0 + c) * K + k0 + kk]) : 0.f;
-            if (GATED) Ws[1][c][kk] = ok ? to_f32<TW>(we[(size_t)(N + n0 + c) * K + k0 + kk]) : 0.f;
+            const bool ok = n0 + c < Ntot && k0 + kk < K;
+            Ws[c][kk] = ok ? to_f32<TW>(we[(size_t)(n0 + c) * K + k0 + kk]) : 0.f;
         }
         __syncthreads();
 #pragma unroll 8
@@ -208,13 +238,11 @@ moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict_
 #pragma unroll
             for (int i = 0; i < RM; ++i) av[i] = As[ty + 16 * i][kk];
 #pragma unroll
-            for (int h = 0; h < (GATED ? 2 : 1); ++h)
+            for (int j = 0; j < RN; ++j) {
+                const float bv = Ws[2 * tx + (j & 1) + 32 * (j >> 1)][kk];
 #pragma unroll
-                for (int j = 0; j < RN; ++j) {
-                    const float bv = Ws[h][tx + 16 * j][kk];
-#pragma unroll
-                    for (int i = 0; i < RM; ++i) acc[h][i][j] = fmaf(av[i], bv, acc[h][i][j]);
-                }
+                for (int i = 0; i < RM; ++i) acc[i][j] = fmaf(av[i], bv, acc[i][j]);
+            }
         }
         __syncthreads();
     }
@@ -224,11 +252,16 @@ moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict_
         if (r >= n_rows) continue;
 #pragma unroll
         for (int j = 0; j < RN; ++j) {
-            const int n = n0 + tx + 16 * j;
-            if (n >= N) continue;
-            float v = acc[0][i][j];
-            if (GATED) v = v / (1.0f + expf(-v)) * acc[1][i][j];
-            out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v);
+            const int n = n0 + 2 * tx + (j & 1) + 32 * (j >> 1);
+            if (n >= Ntot) continue;
+            float v = acc[i][j];
+            if (GATED) {
+                if (j & 1) continue;                                   // the pair's gate writes
+                v = v / (1.0f + expf(-v)) * acc[i][j + 1];
+                out[(size_t)(row0 + r) * out_stride + (n >> 1)] = from_f32<TO>(v);
+            } else {
+                out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v);
+            }
         }
     }
 }
@@ -258,8 +291,8 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int BM, bool GATED> constexpr size_t moe_mma_smem() {
-    return (size_t)TSTAGES * (BM + (GATED ? 2 : 1) * GBN) * TROW * sizeof(bf16);
+template <int BM> constexpr size_t moe_mma_smem() {
+    return (size_t)TSTAGES * (BM + GBN) * TROW * sizeof(bf16);
 }
 
 template <typename TO, int BM, bool GATED>
@@ -270,8 +303,7 @@ moe_product_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
     pdl_trigger();
     pdl_wait();
     constexpr int MB = BM / 16;                            // 16-row blocks
-    constexpr int NW = GATED ? 2 : 1;                      // matrices a tile reads
-    constexpr int STAGE = (BM + NW * GBN) * TROW;          // elements a stage
+    constexpr int STAGE = (BM + GBN) * TROW;               // elements a stage
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sm = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int s_tile[3];
@@ -307,21 +339,18 @@ moe_product_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
             const bool ok = src >= 0 && k0 + ch * 8 < K;
             cp_async16(As + r * TROW + ch * 8, ok ? a + (size_t)src * a_stride + k0 + ch * 8 : a, ok);
         }
-        for (int c = tid; c < NW * GBN * (TBK / 8); c += 128) {
-            const int r = c >> 3, ch = c & 7;              // r: 0..63 first matrix, 64..127 second
-            const int half = r / GBN, col = r - half * GBN;
-            const bool ok = n0 + col < N && k0 + ch * 8 < K;
-            cp_async16(Ws + r * TROW + ch * 8, ok ? we + (size_t)(half * N + n0 + col) * K + k0 + ch * 8 : we, ok);
+        for (int c = tid; c < GBN * (TBK / 8); c += 128) {
+            const int r = c >> 3, ch = c & 7;
+            const bool ok = n0 + r < Ntot && k0 + ch * 8 < K;
+            cp_async16(Ws + r * TROW + ch * 8, ok ? we + (size_t)(n0 + r) * K + k0 + ch * 8 : we, ok);
         }
     };
 
-    float acc[NW][MB][2][4];
+    float acc[MB][2][4];
 #pragma unroll
-    for (int h = 0; h < NW; ++h)
+    for (int m = 0; m < MB; ++m)
 #pragma unroll
-        for (int m = 0; m < MB; ++m)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) acc[h][m][j][0] = acc[h][m][j][1] = acc[h][m][j][2] = acc[h][m][j][3] = 0.f;
+        for (int j = 0; j < 2; ++j) acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f;
 
 #pragma unroll
     for (int st = 0; st < TSTAGES - 1; ++st) {
@@ -337,19 +366,14 @@ moe_product_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
         const bf16* Ws = As + BM * TROW;
 #pragma unroll
         for (int ks = 0; ks < TBK / 16; ++ks) {
-            unsigned bfr[NW][4];
-#pragma unroll
-            for (int h = 0; h < NW; ++h)
-                ldmatrix_x4(bfr[h], Ws + (h * GBN + warp * 16 + (lane & 7) + (lane >> 4) * 8) * TROW + ks * 16 + ((lane >> 3) & 1) * 8);
+            unsigned bfr[4];
+            ldmatrix_x4(bfr, Ws + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * TROW + ks * 16 + ((lane >> 3) & 1) * 8);
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
                 unsigned af[4];
                 ldmatrix_x4(af, As + (m * 16 + (lane & 15)) * TROW + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-                for (int h = 0; h < NW; ++h) {
-                    mma_bf16(acc[h][m][0], af, bfr[h][0], bfr[h][1]);
-                    mma_bf16(acc[h][m][1], af, bfr[h][2], bfr[h][3]);
-                }
+                mma_bf16(acc[m][0], af, bfr[0], bfr[1]);
+                mma_bf16(acc[m][1], af, bfr[2], bfr[3]);
             }
         }
     }
@@ -362,15 +386,31 @@ moe_product_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
             for (int half = 0; half < 2; ++half) {
                 const int r = m * 16 + (lane >> 2) + 8 * half;
                 if (r >= n_rows) continue;
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const int n = n0 + warp * 16 + j * 8 + (lane & 3) * 2 + c;
-                    if (n >= N) continue;
-                    float v = acc[0][m][j][2 * half + c];
-                    if (GATED) v = v / (1.0f + __expf(-v)) * acc[NW - 1][m][j][2 * half + c];
-                    out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v);
+                // a thread holds two neighbouring columns: of a gated matrix, a gate and its up
+                const int n = n0 + warp * 16 + j * 8 + (lane & 3) * 2;
+                const float v0 = acc[m][j][2 * half], v1 = acc[m][j][2 * half + 1];
+                if (GATED) {
+                    if (n + 1 < Ntot) out[(size_t)(row0 + r) * out_stride + (n >> 1)] = from_f32<TO>(v0 / (1.0f + __expf(-v0)) * v1);
+                } else {
+                    if (n < Ntot) out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v0);
+                    if (n + 1 < Ntot) out[(size_t)(row0 + r) * out_stride + n + 1] = from_f32<TO>(v1);
                 }
             }
+}
+
+// ------------------------------------------------------------------------------- gather
+// out[p][:] = x[order[p] / top][:]: the tokens' rows in expert order, for products that want their rows in one
+// piece (16-byte copies; d a multiple of 8).
+__global__ void moe_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ order, int top,
+                                  bf16* __restrict__ out, int rows, int d) {
+    pdl_trigger();
+    pdl_wait();
+    const int chunks = d >> 3;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * chunks;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / chunks), c = (int)(i - (long long)r * chunks);
+        reinterpret_cast<uint4*>(out + (size_t)r * d)[c] = reinterpret_cast<const uint4*>(x + (size_t)(order[r] / top) * d)[c];
+    }
 }
 
 // ------------------------------------------------------------------------------ combine
@@ -395,16 +435,24 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
 
 }  // namespace
 
-RI_API int ri_moe_route(const float* z, const float* correction, int T, int E, int top, int n_groups, int keep,
+// Either z (fp32 [T][E]) or x ([T][d] of x_dtype) with router (fp32 [E][d]) is given.
+RI_API int ri_moe_route(const float* z, const void* x, int x_dtype, const float* router, int d, const float* correction,
+                        int T, int E, int top, int n_groups, int keep,
                         int renorm, int* ids, float* weights, int* counts, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > 32 || (n_groups > 0 && (E % n_groups || keep <= 0 || keep > n_groups)))
         return (int)cudaErrorInvalidValue;
-    const int warps = 4;
-    const size_t smem = (size_t)warps * (2 * E + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
+    const int warps = ROUTE_WARPS;
+    const size_t smem = (size_t)(2 * E + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    RI_CHECKED(ri_launch(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, (cudaStream_t)stream,
-                         z, correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts));
+    if ((z == nullptr) == (x == nullptr) || (x && !router)) return (int)cudaErrorInvalidValue;
+    const dim3 grid(T);
+    if (x && x_dtype == RI_BF16)
+        RI_CHECKED(ri_launch(moe_route_kernel<bf16>, grid, dim3(32 * warps), smem, (cudaStream_t)stream, z, (const bf16*)x, router, d,
+                             correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts));
+    else
+        RI_CHECKED(ri_launch(moe_route_kernel<float>, grid, dim3(32 * warps), smem, (cudaStream_t)stream, z, (const float*)x, router, d,
+                             correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts));
     return ri_launch_status();
 }
 
@@ -430,7 +478,7 @@ RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* 
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int bm = ri_moe_product_rows(rows, E);
-    const dim3 grid((rows + bm - 1) / bm + E, (N + GBN - 1) / GBN);
+    const dim3 grid((rows + bm - 1) / bm + E, ((gated ? 2 * N : N) + GBN - 1) / GBN);
 #define RI_MP(TA, TW, TO, BM, G) RI_CHECKED(ri_launch(moe_product_kernel<TA, TW, TO, BM, G>, grid, dim3(256), 0, s, (const TA*)a, \
         a_stride, (const TW*)w, (TO*)out, out_stride, offsets, order, top, gather, E, N, K))
 #define RI_MP_BM(TA, TW, TO, G) do { if (bm == 64) RI_MP(TA, TW, TO, 64, G); else RI_MP(TA, TW, TO, 16, G); } while (0)
@@ -439,7 +487,7 @@ RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* 
     if (tensor_cores && ((gated && out_dtype == RI_BF16) || (!gated && out_dtype == RI_F32))) {
 #define RI_MM(TO, BM, G) do { \
         static bool configured = false; \
-        const size_t smem = moe_mma_smem<BM, G>(); \
+        const size_t smem = moe_mma_smem<BM>(); \
         if (!configured) { \
             cudaError_t ce = cudaFuncSetAttribute(moe_product_mma_kernel<TO, BM, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (ce != cudaSuccess) return (int)ce; \
@@ -458,6 +506,16 @@ RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* 
     else return (int)cudaErrorInvalidValue;
 #undef RI_MP_BM
 #undef RI_MP
+    return ri_launch_status();
+}
+
+RI_API int ri_moe_gather(const void* x, const int* order, int top, void* out, int rows, int d, void* stream) {
+    if (rows <= 0) return 0;
+    if (d % 8 || ((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+    const long long items = (long long)rows * (d / 8);
+    const int blocks = (int)((items + 255) / 256 < 8192 ? (items + 255) / 256 : 8192);
+    RI_CHECKED(ri_launch(moe_gather_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x, order, top,
+                         (bf16*)out, rows, d));
     return ri_launch_status();
 }
 

@@ -430,10 +430,16 @@ def attention_single_supports(num_heads: int, num_kv_heads: int, head_dim: int, 
 def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      cu_q: torch.Tensor, kv_len: torch.Tensor, entry_list: torch.Tensor, num_heads: int,
                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                     block: Optional[int] = None, value_dim: Optional[int] = None, sink: bool = False) -> None:
+                     block: Optional[int] = None, value_dim: Optional[int] = None, sink: bool = False,
+                     splits: int = 1, part: Optional[torch.Tensor] = None) -> None:
     """Attention of the entries that bring one token (`entry_list`, int32; -1 skips): fp32 arithmetic, a kv
-    head's keys and values read once for all its query heads.  Arguments as `attention_plain`."""
-    require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list)
+    head's keys and values read once for all its query heads.  Arguments as `attention_plain`.  `splits` > 1
+    cuts every entry's keys into that many ranges, a CTA each, joined by a second launch through `part`
+    (fp32, `attention_single_scratch_floats` long)."""
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list, part)
+    if splits > 1 and (part is None or part.dtype != torch.float32 or not part.is_contiguous() or
+                       part.numel() < attention_single_scratch_floats(entry_list.numel(), num_heads, value_dim or head_dim, splits)):
+        raise KernelError("attention_single: the scratch for the key ranges is too small")
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"), (entry_list, "entry_list")):
         _i32(t, n)
     if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != cache.dtype or out.dtype != cache.dtype:
@@ -446,8 +452,12 @@ def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                                   _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list),
                                   entry_list.numel(), num_heads, num_kv_heads, page_size, float(scale),
                                   int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
-                                  stream_ptr()),
-          "attention_single")
+                                  int(splits), _p(part) if splits > 1 else None, stream_ptr()),
+          "attention_single", 2 if splits > 1 else 1)
+
+
+def attention_single_scratch_floats(entries: int, num_heads: int, value_dim: int, splits: int) -> int:
+    return entries * num_heads * splits * (value_dim + 2)
 
 
 def paged_cache_page_size(cache: torch.Tensor, num_kv_heads: int, head_dim: int, value_dim: int) -> int:
@@ -638,19 +648,33 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optio
 
 
 # ------------------------------------------------------------------------ routed experts
-def moe_route(z: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int, keep: int, renorm: bool,
-              ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor) -> None:
-    """Router logits z [T, E] fp32 -> the `top` experts of every token (ids int32 [T, top]) and their weights
-    (fp32 [T, top]): scores sigmoid(z), chosen by score + correction among the experts of the `keep` best of
+def moe_route(z: Optional[torch.Tensor], correction: Optional[torch.Tensor], top: int, n_groups: int, keep: int, renorm: bool,
+              ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor, x: Optional[torch.Tensor] = None,
+              router: Optional[torch.Tensor] = None) -> None:
+    """The `top` experts of every token (ids int32 [T, top]) and their weights (fp32 [T, top]) from router logits:
+    either z [T, E] fp32 is given, or x [T, d] and the router's matrix (fp32 [E, d]) and the kernel forms z = x W^T
+    itself in fp32.  Scores sigmoid(z), chosen by score + correction among the experts of the `keep` best of
     `n_groups` groups (0: no groups).  counts (int32 [E]) gets one added per choice."""
-    require_cuda(z, correction, ids, weights, counts)
-    T, E = z.shape
-    _contig(z, "z"); _contig(ids, "ids"); _contig(weights, "weights"); _i32(ids, "ids"); _i32(counts, "counts")
-    if z.dtype != torch.float32 or weights.dtype != torch.float32 or ids.shape != (T, top) or weights.shape != (T, top) \
-            or counts.numel() != E or (correction is not None and (correction.dtype != torch.float32 or correction.numel() != E)):
-        raise KernelError("moe_route: z fp32 [T, E], correction fp32 [E], ids int32 and weights fp32 [T, top], counts [E]")
-    check(L.core().ri_moe_route(_p(z), _p(correction), T, E, int(top), int(n_groups), int(keep), 1 if renorm else 0,
-                                _p(ids), _p(weights), _p(counts), stream_ptr()), "moe_route")
+    require_cuda(z, correction, ids, weights, counts, x, router)
+    E = counts.numel()
+    T = ids.shape[0]
+    _contig(ids, "ids"); _contig(weights, "weights"); _i32(ids, "ids"); _i32(counts, "counts")
+    if (z is None) == (x is None):
+        raise KernelError("moe_route: give the logits or the router's input, not both")
+    if z is not None and (z.dtype != torch.float32 or z.shape != (T, E) or not z.is_contiguous()):
+        raise KernelError("moe_route: z is contiguous fp32 [T, E]")
+    d = 0
+    if x is not None:
+        d = x.shape[1]
+        if router is None or router.dtype != torch.float32 or tuple(router.shape) != (E, d) or not router.is_contiguous() \
+                or not x.is_contiguous() or x.shape[0] != T:
+            raise KernelError("moe_route: x is contiguous [T, d] and the router's matrix fp32 [E, d]")
+    if weights.dtype != torch.float32 or ids.shape != (T, top) or weights.shape != (T, top) \
+            or (correction is not None and (correction.dtype != torch.float32 or correction.numel() != E)):
+        raise KernelError("moe_route: correction fp32 [E], ids int32 and weights fp32 [T, top], counts [E]")
+    check(L.core().ri_moe_route(_p(z), _p(x), dtype_code(x.dtype) if x is not None else 0, _p(router), d, _p(correction), T, E,
+                                int(top), int(n_groups), int(keep), 1 if renorm else 0, _p(ids), _p(weights), _p(counts),
+                                stream_ptr()), "moe_route")
 
 
 def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
@@ -668,8 +692,8 @@ def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, ord
 def moe_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: Optional[torch.Tensor],
                 top: int, gated: bool) -> None:
     """Rows in expert order times their expert's matrix w [E, Ntot, K]: row p is a[order[p] // top] when `order`
-    is given, else a[p].  gated: Ntot = 2N, out[p] = silu(a w_e[:N]^T) * (a w_e[N:]^T); else out[p] = a w_e^T.
-    fp32 sums in the order of k."""
+    is given, else a[p].  gated: Ntot = 2N and the rows of w_e alternate gate_n, up_n: out[p][n] =
+    silu(a . w_e[2n]) * (a . w_e[2n+1]); else out[p] = a w_e^T.  fp32 sums in the order of k."""
     require_cuda(a, w, out, offsets, order)
     _contig(w, "w"); _i32(offsets, "offsets"); _i32(order, "order")
     E, Ntot, Kd = w.shape
@@ -682,6 +706,40 @@ def moe_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: to
                                   dtype_code(out.dtype), out.stride(0), _p(offsets), _p(order), int(top),
                                   1 if order is not None else 0, rows, E, N, Kd, 1 if gated else 0, stream_ptr()),
           "moe_product")
+
+
+def moe_gather(x: torch.Tensor, order: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    """out[p] = x[order[p] // top]: the tokens' rows (bf16, a multiple of 8 wide) in expert order."""
+    require_cuda(x, order, out)
+    _contig(x, "x"); _contig(out, "out"); _i32(order, "order")
+    if x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or out.shape != (order.numel(), x.shape[1]) or x.shape[1] % 8:
+        raise KernelError("moe_gather: bf16 x [T, d] and out [rows, d] with d a multiple of 8")
+    check(L.core().ri_moe_gather(_p(x), _p(order), int(top), _p(out), out.shape[0], x.shape[1], stream_ptr()), "moe_gather")
+
+
+def gemm_tc_grouped_supports(rows: int, n: int, k: int) -> bool:
+    """Whether `gemm_tc_grouped` takes rows of k against matrices of n rows (TMA wants 16-byte row pitches)."""
+    return k % 8 == 0 and n % 8 == 0
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, epilogue: int) -> None:
+    """Rows in groups against a matrix per group on the tcgen05 tensor cores: x [rows, K] bf16 holds the groups one
+    after the other (group e: rows offsets[e] .. offsets[e+1]-1, int32 on the device), w [E, N, K] bf16.  EPI_F32 /
+    EPI_BF16 store into out [rows, N]; EPI_SILU stores silu(gate) * up of matrices whose rows alternate gate_j, up_j
+    into out [rows, N/2]."""
+    require_cuda(x, w, out, offsets)
+    _contig(x, "x"); _contig(w, "w"); _contig(out, "out"); _i32(offsets, "offsets")
+    E, N, Kd = w.shape
+    rows = x.shape[0]
+    cols = N // 2 if epilogue == EPI_SILU else N
+    want = torch.float32 if epilogue == EPI_F32 else torch.bfloat16
+    if (x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[1] != Kd or Kd % 8 or x.data_ptr() % 16
+            or w.data_ptr() % 16 or out.dtype != want or out.shape != (rows, cols) or offsets.numel() != E + 1
+            or epilogue not in (EPI_BF16, EPI_F32, EPI_SILU)):
+        raise KernelError(f"gemm_tc_grouped: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} {out.dtype}")
+    err = gemm_tc_state(x.device)[2]
+    check(L.gemm_tc().ri_gemm_tc_grouped(_p(x), _p(w), rows, N, Kd, _p(out), out.stride(0), int(epilogue), _p(offsets), E,
+                                         _p(err), stream_ptr()), "gemm_tc_grouped")
 
 
 def moe_combine(Y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],

@@ -39,13 +39,15 @@ _SIGNATURES = {
     "ri_decode_chain": [_P, _I, _P, _I, _P, _P, _I, _P],
     "ri_decode_chain_fits": [_P, _I, _I, _I],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
-    "ri_attention_single": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ri_attention_single": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _P],
     "ri_embed_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
     "ri_hyper_collect": [_P, _I, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _I, _P],
     "ri_qkv_prepare": [_P, _I, _I, _P, _P, _P, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "ri_moe_route": [_P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "ri_moe_route": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "ri_moe_sort": [_P, _P, _I, _I, _P, _P, _P, _P],
     "ri_moe_product": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ri_moe_gather": [_P, _P, _I, _P, _I, _I, _P],
+    "ri_gemm_tc_grouped": [_P, _P, _I, _I, _I, _P, _I, _I, _P, _I, _P, _P],
     "ri_moe_combine": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P],
     "ri_attention_single_supports": [_I, _I],
     "ri_embed_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],

@@ -158,6 +158,12 @@ class GQAAttention(Mixer):
                 and os.environ.get("RUSTINFER_B200_BLOCK_ATTENTION", "fast") != "plain")
         self.precise_mma = (fast and self.vd == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= L.MMA_MAX_HEAD_DIM)
         self.fast_single = fast and K.attention_single_supports(self.Hq, self.Hkv, self.hd, self.vd)
+        if self.fast_single:
+            key = ("single_scratch", self.Hq, self.vd)
+            if key not in ctx.shared:
+                n = K.attention_single_scratch_floats(ctx.max_batch_seqs, self.Hq, self.vd, self.MAX_SPLITS)
+                ctx.shared[key] = torch.empty(n, dtype=torch.float32, device=ctx.device)
+            self.single_part = ctx.shared[key]
         if self.precise_mma or self.fast_single:
             self._single = single_token_entries()
             rows = K.mma_tokens_per_tile(self.Hq, self.Hkv) if self.precise_mma else 16
@@ -279,7 +285,8 @@ class GQAAttention(Mixer):
             (single,) = step.index(self._single)
             if single.numel() and self.fast_single:
                 K.attention_single(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single, self.Hq, self.Hkv,
-                                   self.hd, self.scale, self.window, self.block, self.vd, sink=self.sink)
+                                   self.hd, self.scale, self.window, self.block, self.vd, sink=self.sink,
+                                   splits=self._single_splits(single.numel(), step.max_kv_len), part=self.single_part)
             elif single.numel():                      # every single token is a tile of one row
                 K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single,
                                   self._zeros[: single.numel()], self.Hq, self.Hkv, self.hd, self.scale,
@@ -312,6 +319,18 @@ class GQAAttention(Mixer):
             prefill(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
                     self.Hq, self.Hkv, self.hd, self.scale, self.window)
         return out
+
+    def _single_splits(self, n_single: int, max_kv_len: int) -> int:
+        """Ranges the fp32-arithmetic kernel for single tokens cuts an entry's keys into: enough CTAs for two
+        an SM, no range shorter than 128 keys.  A CTA walks its keys in order, so few CTAs with many keys
+        each are bound by the latency of that walk (1,024 keys a CTA: 131 us for 64 entries of 4 kv heads)."""
+        span = max_kv_len
+        if self.window:
+            span = min(span, self.window)
+        if self.block:
+            span = min(span, self.block)
+        want = -(-2 * self.ctx.num_sms // max(1, n_single * self.Hkv))
+        return max(1, min(want, -(-span // 128), self.MAX_SPLITS))
 
     def _splits(self, n_decode: int, max_kv_len: int) -> int:
         """Ranges each decoding request's keys are cut into.  A few CTAs sit on an SM (the

@@ -14,13 +14,13 @@ captured in a step's CUDA graph.  The reference engine has dense feed-forwards o
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
 
 from ..ops import kernels as K
 from .base import FEED_FORWARDS, FeedForward, ParamDecl, StepContext, register_feed_forward
-from .linear import Linear
 from .spec import PartSpec
 
 
@@ -31,6 +31,8 @@ class RoutedExperts(FeedForward):
     the choice), renormalize, output ("float32", the default, or the activation dtype); tensor names:
     expert_prefix (default "e{}."; `{}` is the expert's number), gate_name / up_name / down_name (default
     "gate" / "up" / "down"), router_name ("router"), correction_name ("correction"), shared_prefix ("shared.")."""
+
+    TC_ROWS_PER_EXPERT = 24              # rows an expert on average from which the tcgen05 products pay
 
     def __init__(self, params):
         super().__init__(params)
@@ -88,23 +90,29 @@ class RoutedExperts(FeedForward):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
         pre = [self.expert_prefix.format(e) for e in range(self.E)]
-        # per expert the gate rows, then the up rows: [E, 2 ff, hidden]; the down matrices [E, hidden, ff]
-        self.gate_up = torch.stack([torch.cat([tensors[p + n["gate"]], tensors[p + n["up"]]], dim=0) for p in pre]).contiguous()
+        # per expert the rows alternate gate_j, up_j, so that a product's epilogue has both of a pair at hand:
+        # [E, 2 ff, hidden]; the down matrices [E, hidden, ff]
+        self.gate_up = torch.stack([torch.stack([tensors[p + n["gate"]], tensors[p + n["up"]]], dim=1)
+                                   .reshape(2 * self.ff, self.hidden) for p in pre]).contiguous()
         self.down = torch.stack([tensors[p + n["down"]] for p in pre]).contiguous()
-        # the router is 32-bit in both engines: its product goes through the exact fp32 kernel
-        self.router = Linear(tensors[n["router"]].to(torch.float32), self.ctx.num_sms)
+        # the router is 32-bit in both engines; the choice kernel forms its product itself
+        self.router = tensors[n["router"]].to(torch.float32).contiguous()
         self.correction = tensors[n["correction"]].to(torch.float32).contiguous() if self.has_correction else None
         self.counts = torch.zeros(self.E, dtype=torch.int32, device=self.gate_up.device)   # the kernels leave it zero
+        self.tensor_memory = (self.gate_up.dtype == torch.bfloat16 and self.gate_up.is_cuda
+                              and K.gemm_tc_grouped_supports(0, 2 * self.ff, self.hidden)
+                              and K.gemm_tc_grouped_supports(0, self.hidden, self.ff)
+                              and os.environ.get("RUSTINFER_B200_EXPERTS", "tc") != "mma")
         if self.shared is not None:
             self.shared.load({local: tensors[self.shared_prefix + name] for local, name in self._shared_names.items()})
 
     def route(self, x: torch.Tensor):
         """(ids int32 [T, top], weights fp32 [T, top]); adds the choices to `self.counts`."""
         T = x.shape[0]
-        z = self.router(x, out_dtype=torch.float32)
         ids = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
-        K.moe_route(z, self.correction, self.top, self.groups, self.keep, self.renorm, ids, weights, self.counts)
+        K.moe_route(None, self.correction, self.top, self.groups, self.keep, self.renorm, ids, weights, self.counts,
+                    x=x if x.is_contiguous() else x.contiguous(), router=self.router)
         return ids, weights
 
     def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None):
@@ -116,10 +124,19 @@ class RoutedExperts(FeedForward):
         place = torch.empty(N, dtype=torch.int32, device=dev)
         K.moe_sort(ids, self.counts, offsets, order, place)
         mid = torch.empty((N, self.ff), dtype=self.gate_up.dtype, device=dev)
-        K.moe_product(x if x.dtype == self.gate_up.dtype else x.to(self.gate_up.dtype), self.gate_up, mid, offsets,
-                      order, self.top, gated=True)
         Y = torch.empty((N, self.hidden), dtype=torch.float32, device=dev)
-        K.moe_product(mid, self.down, Y, offsets, None, self.top, gated=False)
+        xin = x if x.dtype == self.gate_up.dtype else x.to(self.gate_up.dtype)
+        if (self.tensor_memory and N >= self.TC_ROWS_PER_EXPERT * self.E and xin.dtype == torch.bfloat16
+                and xin.is_contiguous()):
+            # many rows an expert: the rows gathered into expert order, both products on tcgen05 with TMA-fed
+            # tiles of 128 rows that never cross from one expert's rows into the next one's results
+            xs = torch.empty((N, self.hidden), dtype=torch.bfloat16, device=dev)
+            K.moe_gather(xin, order, self.top, xs)
+            K.gemm_tc_grouped(xs, self.gate_up, mid, offsets, K.EPI_SILU)
+            K.gemm_tc_grouped(mid, self.down, Y, offsets, K.EPI_F32)
+        else:
+            K.moe_product(xin, self.gate_up, mid, offsets, order, self.top, gated=True)
+            K.moe_product(mid, self.down, Y, offsets, None, self.top, gated=False)
         shared = self.shared.forward(x, step) if self.shared is not None else None
         out = torch.empty((T, self.hidden), dtype=torch.float32 if self.out_fp32 else self.ctx.dtype, device=dev)
         K.moe_combine(Y, place, weights, shared, out, self.counts)

@@ -215,10 +215,12 @@ def test_sink_attention_edges_and_far_keys(dk, dv, window):
                             i32([first + count]), i32([0] * len(tiles)), i32(tiles), H, G, d1, 1.0, window, None, dv, sink=True)
         return out.cpu().view(count, H, dv)
 
-    def attend_single(pos, tgt):
+    def attend_single(pos, tgt, splits=1):
+        """The kernel for entries of one token; with `splits`, the keys in that many ranges joined by a second launch."""
         out = torch.empty((1, H * dv), dtype=torch.float32, device=DEV)
+        part = torch.full((K().attention_single_scratch_floats(1, H, dv, splits),), float("nan"), device=DEV)
         K().attention_single(queries([tgt]).reshape(1, H * d1).to(DEV), out, cache, bt, i32([0, 1]), i32([pos + 1]),
-                             i32([0]), H, G, d1, 1.0, window, None, dv, sink=True)
+                             i32([0]), H, G, d1, 1.0, window, None, dv, sink=True, splits=splits, part=part)
         return out.cpu().view(H, dv)
 
     w = window or 10 ** 9
@@ -239,7 +241,8 @@ def test_sink_attention_edges_and_far_keys(dk, dv, window):
         ref = plain_rows(p, [tgt])[0]
         assert float((attend(p, [tgt])[0].to(F64) - ref).abs().max()) < 2e-4, (p, tgt)
         if K().attention_single_supports(H, G, d1, dv):
-            assert float((attend_single(p, tgt).to(F64) - ref).abs().max()) < 2e-4, (p, tgt)
+            for splits in (1, 2, 5):                       # with 5, ranges of 64 keys: some are empty
+                assert float((attend_single(p, tgt, splits).to(F64) - ref).abs().max()) < 2e-4, (p, tgt, splits)
 
 
 @pytest.mark.parametrize("hd,H,G,window", [(32, 4, 2, 24), (64, 6, 1, 50), (16, 2, 2, None)])
@@ -303,9 +306,21 @@ def test_router_choice(E, top, groups):
     assert torch.equal(got, chosen)                                       # in the order of their choice scores
     assert rel_err(wts, weight) < 1e-6
     assert torch.equal(counts.cpu().long(), torch.bincount(chosen.reshape(-1), minlength=E))
+    # the same from the router's input: the kernel forms the logits itself, in fp32 from a bf16 input
+    d = 83
+    x = rnd(T, d, seed=7).to(torch.bfloat16)
+    rw = rnd(E, d, seed=8, scale=0.5)
+    counts.zero_()
+    K().moe_route(None, corr.to(DEV), top, groups[0] if groups else 0, groups[1] if groups else 0, False, ids, wts, counts,
+                  x=x.to(DEV), router=rw.to(DEV))
+    chosen, weight = P.route(x.to(F64), {"router": rw.to(F64), "correction": corr.to(F64)}, r)
+    same = (ids.cpu().long().sort(dim=1).values == chosen.sort(dim=1).values).all(dim=1)
+    assert float(same.double().mean()) > 0.97                   # a close call may fall the other way in fp32
+    assert rel_err(wts[same.to(DEV)], weight[same]) < 1e-5
 
 
-@pytest.mark.parametrize("T,E,top,d,ff", [(150, 8, 3, 96, 40), (5, 6, 2, 83, 24), (700, 4, 1, 64, 72), (1, 3, 3, 64, 20)])
+@pytest.mark.parametrize("T,E,top,d,ff", [(150, 8, 3, 96, 40), (5, 6, 2, 83, 24), (700, 4, 1, 64, 72), (1, 3, 3, 64, 20),
+                                          (600, 5, 2, 320, 136)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_experts_sort_products_and_sum(T, E, top, d, ff, dtype):
     """Pairs sorted by expert keep their order; every row meets its own expert's matrices; the weighted sum comes
@@ -332,9 +347,22 @@ def test_experts_sort_products_and_sum(T, E, top, d, ff, dtype):
     assert torch.equal(place.cpu().long()[want_order], torch.arange(N))
     assert offsets.cpu().tolist() == [0] + torch.cumsum(torch.bincount(flat, minlength=E), 0).tolist()
     mid = torch.empty((N, ff), dtype=dtype, device=DEV)
-    K().moe_product(x.to(DEV), gate_up.to(DEV), mid, offsets, order, top, gated=True)
+    laced = torch.stack([gate_up[:, :ff], gate_up[:, ff:]], dim=2).reshape(E, 2 * ff, d).contiguous()   # gate_j, up_j, ...
+    K().moe_product(x.to(DEV), laced.to(DEV), mid, offsets, order, top, gated=True)
     Y = torch.empty((N, d), dtype=torch.float32, device=DEV)
     K().moe_product(mid, down.to(DEV), Y, offsets, None, top, gated=False)
+    if dtype == torch.bfloat16 and d % 8 == 0 and ff % 8 == 0:
+        # the same on tcgen05: rows gathered into expert order, tiles of 128 rows, groups that end inside a tile
+        xs = torch.empty((N, d), dtype=dtype, device=DEV)
+        K().moe_gather(x.to(DEV), order, top, xs)
+        assert torch.equal(xs.cpu(), x[order.cpu().long() // top])
+        mid2 = torch.full((N, ff), float("nan"), dtype=dtype, device=DEV)
+        K().gemm_tc_grouped(xs, laced.to(DEV), mid2, offsets, K().EPI_SILU)
+        Y2 = torch.full((N, d), float("nan"), dtype=torch.float32, device=DEV)
+        K().gemm_tc_grouped(mid2, down.to(DEV), Y2, offsets, K().EPI_F32)
+        torch.cuda.synchronize()
+        assert K().gemm_tc_error(torch.device(DEV)) == 0
+        assert rel_err(mid2, mid) < 1e-2 and rel_err(Y2, Y) < 1e-2
     out = torch.empty((T, d), dtype=torch.float32, device=DEV)
     K().moe_combine(Y, place, wts.to(DEV), shared.to(DEV), out, counts)
     assert int(counts.abs().sum()) == 0
