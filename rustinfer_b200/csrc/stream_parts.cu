@@ -43,7 +43,27 @@ __global__ void embed_rmsnorm_kernel(const int* __restrict__ ids, const TE* __re
 // Sums run over s = 0, 1, .. in that order.
 constexpr int MAX_STREAMS = 8;
 
-template <typename TY, typename TW, typename TO>
+// four consecutive elements at index i (a multiple of 4) of a row whose start is 16-byte aligned
+__device__ __forceinline__ void load4(const float* p, int i, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p + i);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, int i, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p + i);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x), b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+__device__ __forceinline__ void store4(float* p, int i, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, int i, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<const unsigned*>(&a); t.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p + i) = t;
+}
+
+template <typename TY, typename TW, typename TO, int VEC>
 __global__ void hyper_collect_kernel(float* __restrict__ X, int fresh, const TY* __restrict__ y,
                                      const float* __restrict__ mix, const float* __restrict__ write,
                                      const float* __restrict__ read, const TW* __restrict__ w, float eps,
@@ -64,32 +84,56 @@ __global__ void hyper_collect_kernel(float* __restrict__ X, int fresh, const TY*
     const int t = rows ? rows[r] : r;
     const size_t plane = (size_t)T * d;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float xs[MAX_STREAMS];
+    // VEC = 4: rows of a multiple of 4 elements, four at a time (16-byte loads of the streams)
+    for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
+        float xs[MAX_STREAMS][VEC];
 #pragma unroll
         for (int s = 0; s < MAX_STREAMS; ++s)
-            if (s < S) xs[s] = X[(fresh ? 0 : (size_t)s * plane) + (size_t)t * d + i];
-        float acc = 0.f;
+            if (s < S) {
+                const float* src = X + (fresh ? 0 : (size_t)s * plane) + (size_t)t * d;
+                if (VEC == 4) load4(src, i, reinterpret_cast<float (&)[4]>(xs[s]));
+                else xs[s][0] = src[i];
+            }
+        float acc[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
         if (y) {
-            const float yv = to_f32<TY>(y[(size_t)t * d + i]);
+            float yv[VEC];
+            if (VEC == 4) load4(y + (size_t)t * d, i, reinterpret_cast<float (&)[4]>(yv));
+            else yv[0] = to_f32<TY>(y[(size_t)t * d + i]);
 #pragma unroll
             for (int to = 0; to < MAX_STREAMS; ++to)
                 if (to < S) {
-                    float n = 0.f;
+                    float n[VEC];
 #pragma unroll
-                    for (int s = 0; s < MAX_STREAMS; ++s)
-                        if (s < S) n = fmaf(s_mix[s * S + to], xs[s], n);
-                    n = fmaf(s_write[to], yv, n);
-                    if (!rows) X[(size_t)to * plane + (size_t)t * d + i] = n;
-                    acc = fmaf(s_read[to], n, acc);
+                    for (int v = 0; v < VEC; ++v) {
+                        float a = 0.f;
+#pragma unroll
+                        for (int s = 0; s < MAX_STREAMS; ++s)
+                            if (s < S) a = fmaf(s_mix[s * S + to], xs[s][v], a);
+                        a = fmaf(s_write[to], yv[v], a);
+                        n[v] = a;
+                        acc[v] = fmaf(s_read[to], a, acc[v]);
+                    }
+                    if (!rows) {
+                        float* dst = X + (size_t)to * plane + (size_t)t * d;
+                        if (VEC == 4) store4(dst, i, reinterpret_cast<const float (&)[4]>(n));
+                        else dst[i] = n[0];
+                    }
                 }
         } else {
 #pragma unroll
             for (int s = 0; s < MAX_STREAMS; ++s)
-                if (s < S) acc = fmaf(s_read[s], xs[s], acc);
+                if (s < S) {
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) acc[v] = fmaf(s_read[s], xs[s][v], acc[v]);
+                }
         }
-        u[i] = acc;
-        ss += acc * acc;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            u[i + v] = acc[v];
+            ss += acc[v] * acc[v];
+        }
     }
     if (!out) return;
     if (!w) {
@@ -99,8 +143,18 @@ __global__ void hyper_collect_kernel(float* __restrict__ X, int fresh, const TY*
     }
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x)
-        out[(size_t)r * d + i] = from_f32<TO>(u[i] * inv * to_f32<TW>(w[i]));
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+            float wv4[4], o[4];
+            load4(w, i, wv4);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) o[v] = u[i + v] * inv * wv4[v];
+            store4(out + (size_t)r * d, i, o);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x)
+            out[(size_t)r * d + i] = from_f32<TO>(u[i] * inv * to_f32<TW>(w[i]));
+    }
 }
 
 // ------------------------------------ q, k, v from the projection to the attention and the cache
@@ -221,8 +275,14 @@ RI_API int ri_hyper_collect(float* X, int fresh, const void* y, int y_dtype, con
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)(d + 33) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-#define RI_HC(TY, TW, TO) RI_CHECKED(ri_launch(hyper_collect_kernel<TY, TW, TO>, dim3(n_rows), dim3(256), smem, s, X, fresh, \
-        (const TY*)y, mix, write, read, (const TW*)w, eps, (TO*)out, rows, T, d, S))
+    const size_t ysz = y_dtype == RI_BF16 ? 2 : 4, wsz = w_dtype == RI_BF16 ? 2 : 4, osz = out_dtype == RI_BF16 ? 2 : 4;
+    const bool vec = d % 4 == 0 && ((uintptr_t)X & 15) == 0 && (!y || ((uintptr_t)y % (4 * ysz)) == 0) &&
+                     (!w || ((uintptr_t)w % (4 * wsz)) == 0) && (!out || ((uintptr_t)out % (4 * osz)) == 0);
+#define RI_HC(TY, TW, TO) do { \
+        if (vec) RI_CHECKED(ri_launch(hyper_collect_kernel<TY, TW, TO, 4>, dim3(n_rows), dim3(256), smem, s, X, fresh, \
+            (const TY*)y, mix, write, read, (const TW*)w, eps, (TO*)out, rows, T, d, S)); \
+        else RI_CHECKED(ri_launch(hyper_collect_kernel<TY, TW, TO, 1>, dim3(n_rows), dim3(256), smem, s, X, fresh, \
+            (const TY*)y, mix, write, read, (const TW*)w, eps, (TO*)out, rows, T, d, S)); } while (0)
 #define RI_HC2(TY, TW) do { if (out_dtype == RI_BF16) RI_HC(TY, TW, bf16); else RI_HC(TY, TW, float); } while (0)
     if (y_dtype == RI_BF16 && w_dtype == RI_BF16) RI_HC2(bf16, bf16);
     else if (y_dtype == RI_BF16) RI_HC2(bf16, float);
