@@ -181,9 +181,18 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
 constexpr int SK = 512;                        // keys per chunk
 constexpr int SG = 16;                         // most query heads a kv head
 constexpr int SV = (VD + 31) / 32;             // value channels a lane
-constexpr size_t SINGLE_SMEM_FLOATS = (size_t)SG * HD + (size_t)SG * SK + 3 * SG + (size_t)(THREADS / 32) * SG * VD;
+// the parts of the weighted sum that meet in shared memory at the end: a warp's (old walk) or, in the wide walk,
+// a thread's (up to 8 heads x 8 channels each)
+constexpr size_t SINGLE_RED_FLOATS = (size_t)(THREADS / 32) * SG * VD > (size_t)THREADS * 64 ? (size_t)(THREADS / 32) * SG * VD
+                                                                                             : (size_t)THREADS * 64;
+constexpr size_t SINGLE_SMEM_FLOATS = (size_t)SG * HD + (size_t)SG * SK + 3 * SG + SINGLE_RED_FLOATS;
 
-template <typename T>
+// GM: the most query heads a kv head this instantiation keeps sums for (4, 8 or 16).  With up to 8 heads, values
+// whose rows are whole 16-byte pieces and a piece count that divides the CTA, the weighted sum runs "wide": a
+// thread owns one 16-byte piece of the value row and every (THREADS / pieces)-th key, so that one load serves
+// 8 (bf16) channels of all heads and 128 loads are in flight a CTA instead of 16; the threads' parts are added
+// in a fixed order at the end.
+template <typename T, int GM>
 __global__ void __launch_bounds__(THREADS)
 attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                         const T* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
@@ -221,15 +230,27 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     for (int e = tid; e < G * HD; e += THREADS)
         qs[e] = to_f32<T>(q[(size_t)t * q_stride + (size_t)kvh * G * HD + e]);
     if (tid < G) { mrun[tid] = sink ? 0.f : -INFINITY; lrun[tid] = sink ? 1.f : 0.f; }
-    float acc[SG][SV];
+    constexpr int VECW = 16 / (int)sizeof(T);               // elements of a 16-byte piece
+    constexpr int PIECES = VD % VECW == 0 ? VD / VECW : 1;  // pieces of a value row
+    constexpr bool WIDE_OK = GM <= 8 && VD % VECW == 0 && THREADS % PIECES == 0 && PIECES <= THREADS;
+    constexpr int KG = WIDE_OK ? THREADS / PIECES : 1;      // keys a pass of the wide walk takes
+    float acc[WIDE_OK ? 1 : GM][SV];
+    float accw[WIDE_OK ? GM : 1][VECW];
 #pragma unroll
-    for (int g = 0; g < SG; ++g)
+    for (int g = 0; g < (WIDE_OK ? 1 : GM); ++g)
 #pragma unroll
         for (int i = 0; i < SV; ++i) acc[g][i] = 0.f;
+#pragma unroll
+    for (int g = 0; g < (WIDE_OK ? GM : 1); ++g)
+#pragma unroll
+        for (int i = 0; i < VECW; ++i) accw[g][i] = 0.f;
     const int* bt = block_table + (size_t)b * table_stride;
     const size_t page_elems = (size_t)Hkv * page_size * (HD + VD);
     const size_t v_base = (size_t)Hkv * page_size * HD + (size_t)kvh * page_size * VD;
     const size_t k_base = (size_t)kvh * page_size * HD;
+    // value rows start on 16-byte boundaries (the cache itself does: the host checks)
+    const bool wide = WIDE_OK && page_elems % VECW == 0 && v_base % VECW == 0;
+    const int piece = tid % PIECES, kgroup = tid / PIECES;
     __syncthreads();
     for (int k0 = lo; k0 <= p; k0 += SK) {
         const int n = min(SK, p - k0 + 1);
@@ -246,13 +267,22 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
                 for (int d0 = 0; d0 < HD; d0 += VEC) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(kp + d0);
                     const T* e = reinterpret_cast<const T*>(&raw);
+                    float kd[VEC];
 #pragma unroll
-                    for (int i = 0; i < VEC; ++i) {
-                        const float kd = to_f32<T>(e[i]);
+                    for (int i = 0; i < VEC; ++i) kd[i] = to_f32<T>(e[i]);
+                    // a head's q comes four channels a shared-memory load (every thread the same address)
 #pragma unroll
-                        for (int g = 0; g < SG; ++g)
-                            if (g < G) s[g] = fmaf(qs[g * HD + d0 + i], kd, s[g]);
-                    }
+                    for (int g = 0; g < SG; ++g)
+                        if (g < G) {
+#pragma unroll
+                            for (int i = 0; i < VEC; i += 4) {
+                                const float4 q4 = *reinterpret_cast<const float4*>(qs + g * HD + d0 + i);
+                                s[g] = fmaf(q4.x, kd[i], s[g]);
+                                s[g] = fmaf(q4.y, kd[i + 1], s[g]);
+                                s[g] = fmaf(q4.z, kd[i + 2], s[g]);
+                                s[g] = fmaf(q4.w, kd[i + 3], s[g]);
+                            }
+                        }
                 }
             } else {
                 for (int d = 0; d < HD; ++d) {
@@ -288,43 +318,100 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
             }
         }
         __syncthreads();
-        // weighted sum of the values: a warp a key, a lane a value channel
+        if (WIDE_OK) {
 #pragma unroll
-        for (int g = 0; g < SG; ++g)
-            if (g < G) {
-                const float a = arun[g];
-#pragma unroll
-                for (int i = 0; i < SV; ++i) acc[g][i] *= a;
-            }
-#pragma unroll 4                                          // the loads of four keys in flight
-        for (int kk = warp; kk < n; kk += WARPS) {
-            const int key = k0 + kk, blk = key / page_size;
-            const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD;
-            float v[SV];
-#pragma unroll
-            for (int i = 0; i < SV; ++i) v[i] = lane + 32 * i < VD ? to_f32<T>(vp[lane + 32 * i]) : 0.f;
-#pragma unroll
-            for (int g = 0; g < SG; ++g)
+            for (int g = 0; g < (WIDE_OK ? GM : 1); ++g)
                 if (g < G) {
-                    const float w = sc[g * SK + kk];
+                    const float a = arun[g];
 #pragma unroll
-                    for (int i = 0; i < SV; ++i) acc[g][i] = fmaf(w, v[i], acc[g][i]);
+                    for (int i = 0; i < VECW; ++i) accw[g][i] *= a;
                 }
+        }
+        if (WIDE_OK && wide) {
+            // weighted sum of the values, wide: a thread a 16-byte piece of every KG-th key's row
+#pragma unroll 4                                          // the loads of four keys in flight a thread
+            for (int kk = kgroup; kk < n; kk += KG) {
+                const int key = k0 + kk, blk = key / page_size;
+                const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD + piece * VECW;
+                const uint4 raw = *reinterpret_cast<const uint4*>(vp);
+                const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int g = 0; g < (WIDE_OK ? GM : 1); ++g)
+                    if (g < G) {
+                        const float w = sc[g * SK + kk];
+#pragma unroll
+                        for (int i = 0; i < VECW; ++i) accw[g][i] = fmaf(w, to_f32<T>(e[i]), accw[g][i]);
+                    }
+            }
+        } else {
+            // weighted sum of the values: a warp a key, a lane a value channel
+#pragma unroll
+            for (int g = 0; g < (WIDE_OK ? 1 : GM); ++g)
+                if (g < G) {
+                    const float a = arun[g];
+#pragma unroll
+                    for (int i = 0; i < SV; ++i) acc[g][i] *= a;
+                }
+            if (!WIDE_OK) {
+#pragma unroll 4                                          // the loads of four keys in flight
+                for (int kk = warp; kk < n; kk += WARPS) {
+                    const int key = k0 + kk, blk = key / page_size;
+                    const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD;
+                    float v[SV];
+#pragma unroll
+                    for (int i = 0; i < SV; ++i) v[i] = lane + 32 * i < VD ? to_f32<T>(vp[lane + 32 * i]) : 0.f;
+#pragma unroll
+                    for (int g = 0; g < (WIDE_OK ? 1 : GM); ++g)
+                        if (g < G) {
+                            const float w = sc[g * SK + kk];
+#pragma unroll
+                            for (int i = 0; i < SV; ++i) acc[g][i] = fmaf(w, v[i], acc[g][i]);
+                        }
+                }
+            } else {
+                // rows that are no whole 16-byte pieces at run time (an odd page or head count): a thread a
+                // piece still, element by element
+                for (int kk = kgroup; kk < n; kk += KG) {
+                    const int key = k0 + kk, blk = key / page_size;
+                    const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD + piece * VECW;
+#pragma unroll
+                    for (int g = 0; g < (WIDE_OK ? GM : 1); ++g)
+                        if (g < G) {
+                            const float w = sc[g * SK + kk];
+#pragma unroll
+                            for (int i = 0; i < VECW; ++i) accw[g][i] = fmaf(w, to_f32<T>(vp[i]), accw[g][i]);
+                        }
+                }
+            }
         }
         __syncthreads();                                 // sc and arun are free for the next chunk
     }
+    if (WIDE_OK) {
+        // a thread's part: [key group][head][piece's channels]
 #pragma unroll
-    for (int g = 0; g < SG; ++g)
-        if (g < G) {
+        for (int g = 0; g < (WIDE_OK ? GM : 1); ++g)
+            if (g < G) {
 #pragma unroll
-            for (int i = 0; i < SV; ++i)
-                if (lane + 32 * i < VD) red[((size_t)warp * SG + g) * VD + lane + 32 * i] = acc[g][i];
-        }
+                for (int i = 0; i < VECW; ++i) red[((size_t)kgroup * GM + g) * VD + piece * VECW + i] = accw[g][i];
+            }
+    } else {
+#pragma unroll
+        for (int g = 0; g < (WIDE_OK ? 1 : GM); ++g)
+            if (g < G) {
+#pragma unroll
+                for (int i = 0; i < SV; ++i)
+                    if (lane + 32 * i < VD) red[((size_t)warp * SG + g) * VD + lane + 32 * i] = acc[g][i];
+            }
+    }
     __syncthreads();
     for (int e = tid; e < G * VD; e += THREADS) {
         const int g = e / VD, d = e - g * VD;
         float total = 0.f;
-        for (int w = 0; w < WARPS; ++w) total += red[((size_t)w * SG + g) * VD + d];
+        if (WIDE_OK) {
+            for (int w = 0; w < KG; ++w) total += red[((size_t)w * GM + g) * VD + d];
+        } else {
+            for (int w = 0; w < WARPS; ++w) total += red[((size_t)w * SG + g) * VD + d];
+        }
         const float l = lrun[g];
         if (splits > 1) {
             float* dst = part + (((size_t)blockIdx.y * Hq + kvh * G + g) * splits + blockIdx.z) * (VD + 2);
@@ -424,15 +511,19 @@ RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_s
     if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
     if (Hq / Hkv > SG || SV > 4) return (int)cudaErrorNotSupported;
     if (splits < 1 || splits > 64 || (splits > 1 && !part)) return (int)cudaErrorInvalidValue;
-    const size_t smem = SINGLE_SMEM_FLOATS * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(Hkv, n_entries, splits);
-#define RI_SINGLE(T) do { static bool configured = false; \
+#define RI_SINGLE(T) do { const int G_ = Hq / Hkv; \
+    if (G_ <= 4) RI_SINGLE_G(T, 4); else if (G_ <= 8) RI_SINGLE_G(T, 8); else RI_SINGLE_G(T, 16); } while (0)
+#define RI_SINGLE_G(T, GM) do { static bool configured = false; \
+    /* the parts' meeting place is as large as this many heads need: fewer heads, more CTAs an SM */ \
+    const size_t wide_red = GM <= 8 ? (size_t)THREADS * GM * 8 : 0, old_red = (size_t)(THREADS / 32) * SG * VD; \
+    const size_t smem = ((size_t)SG * HD + (size_t)SG * SK + 3 * SG + (wide_red > old_red ? wide_red : old_red)) * sizeof(float); \
     if (!configured) { \
-        cudaError_t e = cudaFuncSetAttribute(attention_single_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaError_t e = cudaFuncSetAttribute(attention_single_kernel<T, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e; \
         configured = true; } \
-    RI_CHECKED(ri_launch(attention_single_kernel<T>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (T*)out, \
+    RI_CHECKED(ri_launch(attention_single_kernel<T, GM>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (T*)out, \
         out_stride, (const T*)cache, block_table, table_stride, cu_q, kv_len, entry_list, Hq, Hkv, page_size, scale, \
         window, block, sink, part)); \
     if (splits > 1) RI_CHECKED(ri_launch(attention_single_merge_kernel<T>, dim3(Hq, n_entries), dim3(VD < 64 ? 32 : 64), 0, s, \
@@ -440,6 +531,7 @@ RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_s
     if (dtype == RI_BF16) RI_SINGLE(bf16);
     else RI_SINGLE(float);
 #undef RI_SINGLE
+#undef RI_SINGLE_G
     return ri_launch_status();
 }
 
