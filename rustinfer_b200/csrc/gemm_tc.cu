@@ -320,6 +320,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         int s = 0, t = 0;
         unsigned par = 0;
+        // a grouped product's tiles are found in offsets that the kernels before wrote: this thread reads them too
+        // (otherwise it touches only shared and tensor memory and needs no wait)
+        if (p.grp_offsets) pdl_wait();
         for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x, ++t) {
             if (p.grp_offsets) {
                 int ga0, ga_end, gb0, gfeat0;

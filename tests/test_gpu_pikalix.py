@@ -381,6 +381,52 @@ def test_experts_sort_products_and_sum(T, E, top, d, ff, dtype):
     assert rel_err(out, ref) < (3e-6 if dtype == torch.float32 else 2e-3)
 
 
+def test_grouped_products_follow_the_sort():
+    """The tcgen05 products find their tiles in offsets that the sort before them writes, in buffers that are used
+    again step after step: launched back to back (every kernel may start while its predecessor drains), each round's
+    products must see that round's offsets and no earlier ones."""
+    T, E, top, d, ff = 400, 6, 2, 128, 64
+    g = torch.Generator().manual_seed(3)
+    x = rnd(T, d, seed=1).to(torch.bfloat16).to(DEV)
+    laced = (rnd(E, 2 * ff, d, seed=2) / math.sqrt(d)).to(torch.bfloat16).to(DEV)
+    down = (rnd(E, d, ff, seed=3) / math.sqrt(ff)).to(torch.bfloat16).to(DEV)
+    N = T * top
+    offsets = torch.zeros(E + 1, dtype=torch.int32, device=DEV)
+    order = torch.zeros(N, dtype=torch.int32, device=DEV)
+    place = torch.zeros(N, dtype=torch.int32, device=DEV)
+    xs = torch.empty((N, d), dtype=torch.bfloat16, device=DEV)
+    rounds = []
+    for r in range(6):
+        # very uneven and different every round: most pairs on one expert, which moves
+        ids = torch.full((T, top), r % E, dtype=torch.int64)
+        ids[:, 1] = (r + 1 + torch.randint(0, E - 1, (T,), generator=g)) % E
+        ids[torch.rand(T, generator=g) < 0.3, 0] = (r + 3) % E
+        rounds.append(ids)
+    outs, refs = [], []
+    for ids in rounds:
+        counts = torch.bincount(ids.reshape(-1), minlength=E).to(torch.int32).to(DEV)
+        K().moe_sort(ids.to(torch.int32).to(DEV), counts, offsets, order, place)
+        K().moe_gather(x, order, top, xs)
+        mid = torch.empty((N, ff), dtype=torch.bfloat16, device=DEV)
+        K().gemm_tc_grouped(xs, laced, mid, offsets, K().EPI_SILU)
+        Y = torch.empty((N, d), dtype=torch.float32, device=DEV)
+        K().gemm_tc_grouped(mid, down, Y, offsets, K().EPI_F32)
+        outs.append((Y, place.clone()))
+    torch.cuda.synchronize()
+    assert K().gemm_tc_error(torch.device(DEV)) == 0
+    for ids, (Y, pl) in zip(rounds, outs):
+        counts = torch.bincount(ids.reshape(-1), minlength=E).to(torch.int32).to(DEV)
+        o2, or2, pl2 = torch.empty_like(offsets), torch.empty_like(order), torch.empty_like(place)
+        K().moe_sort(ids.to(torch.int32).to(DEV), counts, o2, or2, pl2)
+        mid = torch.empty((N, ff), dtype=torch.bfloat16, device=DEV)
+        K().moe_product(x, laced, mid, o2, or2, top, gated=True)
+        want = torch.empty((N, d), dtype=torch.float32, device=DEV)
+        K().moe_product(mid, down, want, o2, None, top, gated=False)
+        torch.cuda.synchronize()
+        assert torch.equal(pl, pl2)
+        assert rel_err(Y, want) < 1e-2
+
+
 # ============================================================================ the engine
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
