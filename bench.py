@@ -596,15 +596,15 @@ def dirurax_kernels(hbm_gbs, size):
 
 
 def _pikalix(width, layers, ff, vocab, attn, window, rot, experts, top, expert_ff, shared_ff, groups, streams):
-    """`layers` layers of attention with a sliding window; the second half reads the keys and values of the
-    last layer of the first half; feed-forwards alternate between a dense one and routed experts."""
+    """`layers` layers of attention with a sliding window; every odd layer reads the keys and values of the layer
+    before it; feed-forwards alternate between a dense one and routed experts."""
     h, kv, dim, vdim = attn
     out = []
     for i in range(layers):
         mixer = {"heads": h, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window},
                  "rot": {"dims": rot, "base": 500000.0}}
-        if i >= layers // 2:
-            mixer["kv_from"] = layers // 2 - 1
+        if i % 2 == 1:
+            mixer["kv_from"] = i - 1
         mlp = {"kind": "dense", "ff": ff} if i % 2 == 0 else {
             "kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff},
             "router": {"experts": experts, "top": top, "groups": {"count": groups[0], "keep": groups[1]}}}

@@ -641,3 +641,53 @@ def test_trace_replay_command(models, tmp_path):
     assert rel_err(g1, rb[[18]]) <= TOL["float32"]
     g2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4")).view(2, V)
     assert rel_err(g2, torch.stack([rb[19], ra[69]])) <= TOL["float32"]
+
+
+def test_command_line_and_sampler_serve_a_pikalix_folder(models, tmp_path):
+    """`bin/rustinfer --config run.toml` on a Pikalix folder: greedy tokens are the plain model's.  Through `Engine`
+    with temperature, top-k and top-p: a seeded request gives the same tokens twice, and every drawn token is among
+    the most likely at its place."""
+    import sys
+    from rustinfer_b200.engine.engine import Engine
+    from rustinfer_b200.sampling.params import SamplingParams
+    folder, plain = models["R"]
+    V = CONFIGS["R"]["vocab"]
+    prompt = random_ids(21, V, 8)
+    (tmp_path / "run.toml").write_text(f"""
+model = "{folder}"
+dtype = "float32"
+max_batch_tokens = 64
+max_batch_seqs = 3
+max_model_len = 96
+paged_block_size = 16
+chunked_prefill_size = 8
+num_blocks = 18
+ignore_eos = true
+capture_sizes = [1, 2, 4]
+
+[sampling]
+temperature = 0.0
+max_tokens = 7
+
+[[request]]
+prompt_ids = {prompt}
+
+[[request]]
+prompt_ids = {prompt[:5]}
+""")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "rustinfer"), "--config", str(tmp_path / "run.toml")],
+                       capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.strip()]
+    assert [l["request"] for l in lines] == [0, 1]
+    assert lines[0]["tokens"] == plain.greedy(prompt, 7) and lines[1]["tokens"] == plain.greedy(prompt[:5], 7)
+    eng = Engine(folder, dtype="float32", max_batch_seqs=3, max_model_len=96, paged_block_size=16, num_blocks=18,
+                 max_batch_tokens=64, chunked_prefill_size=8)
+    sp = SamplingParams(temperature=0.9, top_k=12, top_p=0.8, seed=11, max_tokens=7, ignore_eos=True)
+    first = [r.tokens for r in eng.generate([prompt[:5], prompt], sp)]
+    again = [r.tokens for r in eng.generate([prompt[:5], prompt], sp)]
+    assert first == again and all(len(t) == 7 for t in first)
+    ids = list(prompt[:5])
+    for tok in first[0]:
+        assert tok in torch.topk(plain.logits(ids)[-1], 12).indices.tolist()
+        ids.append(tok)
